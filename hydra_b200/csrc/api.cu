@@ -1,0 +1,946 @@
+// api.cu — the C ABI declared in include/hydra_cuda.h: argument checking, the KV-cache object and
+// its bookkeeping, and the choice of kernels for each call.  All device work is in the other files.
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "internal.hpp"
+
+namespace hc {
+
+static thread_local std::string g_last_error = "";
+
+hc_status fail(hc_status status, const std::string& message) {
+    g_last_error = message;
+    return status;
+}
+
+hc_status check_cuda(cudaError_t err, const char* what) {
+    if (err == cudaSuccess) return HC_OK;
+    return fail(HC_CUDA_ERROR, std::string(what) + ": " + cudaGetErrorString(err));
+}
+
+namespace {
+
+int round_up(int value, int multiple) { return (value + multiple - 1) / multiple * multiple; }
+
+size_t dtype_bytes(int dtype) { return dtype == HC_F32 ? 4 : 2; }
+
+// KVCache.linearWindowLimit (Sources/HydraMetal/KVCache.swift:130).
+constexpr int kLinearWindowLimit = 8192;
+
+bool group_ok(int group) { return group == 1 || group == 2 || group == 4 || group == 8 || group == 16; }
+
+hc_status validate_params(const hc_kv_cache* cache, int layer, const hc_attn_params* p) {
+    if (!cache || !p) return fail(HC_INVALID_ARGUMENT, "null cache or params");
+    if (layer < 0 || layer >= int(cache->layers.size())) return fail(HC_INVALID_ARGUMENT, "layer index out of range");
+    const hc_layer_store& L = cache->layers[size_t(layer)];
+    if (!L.keeps_history) {
+        return fail(HC_UNSUPPORTED, "layer " + std::to_string(layer) + " keeps a recurrent state, not a key/value history");
+    }
+    if (p->head_dim != L.desc.head_dim || p->kv_heads != L.desc.kv_heads) {
+        return fail(HC_DIM_MISMATCH, "params geometry differs from the cache layer's");
+    }
+    if (p->q_heads <= 0 || p->q_heads > L.desc.q_heads || p->q_heads % p->kv_heads != 0 ||
+        !group_ok(p->q_heads / p->kv_heads)) {
+        return fail(HC_DIM_MISMATCH, "q_heads must be a power-of-two multiple (<= 16) of kv_heads and no larger than the layer's");
+    }
+    if (p->window != L.desc.window) return fail(HC_DIM_MISMATCH, "params.window differs from the cache layer's window");
+    if (p->io_dtype != HC_F32 && p->io_dtype != HC_BF16) return fail(HC_INVALID_ARGUMENT, "unknown io_dtype");
+    if (p->norm_q == 1 && !p->q_norm_weight) return fail(HC_INVALID_ARGUMENT, "norm_q = 1 without q_norm_weight");
+    if (p->norm_k == 1 && !p->k_norm_weight) return fail(HC_INVALID_ARGUMENT, "norm_k = 1 without k_norm_weight");
+    if (p->norm_v == 1) return fail(HC_INVALID_ARGUMENT, "norm_v takes 0 or 2 (weightless): v_norm has no weight");
+    if (p->rope && p->rope->pairs != p->head_dim / 2) return fail(HC_DIM_MISMATCH, "rope table pairs != head_dim / 2");
+    if (p->gate_layout == HC_GATE_SEPARATE && !p->gate) return fail(HC_INVALID_ARGUMENT, "HC_GATE_SEPARATE without a gate buffer");
+    if (p->gate_layout < HC_GATE_NONE || p->gate_layout > HC_GATE_INTERLEAVED) return fail(HC_INVALID_ARGUMENT, "unknown gate_layout");
+    if (!(p->sm_scale > 0.0f)) return fail(HC_INVALID_ARGUMENT, "sm_scale must be positive");
+    return HC_OK;
+}
+
+CacheView view_of(const hc_kv_cache* cache, const hc_layer_store& L) {
+    CacheView view;
+    view.k = L.k;
+    view.v = L.v;
+    view.capacity = L.capacity;
+    view.kv_heads = L.desc.kv_heads;
+    view.map.ring = L.ring;
+    const bool sequence = cache->shard.mode == HC_SHARD_SEQUENCE && cache->shard.world > 1;
+    view.map.rank = sequence ? cache->shard.rank : 0;
+    view.map.world = sequence ? cache->shard.world : 1;
+    return view;
+}
+
+AttnShape shape_of(const hc_kv_cache* cache, const hc_attn_params* p, bool partial_mode) {
+    AttnShape shape;
+    shape.q_heads = p->q_heads;
+    shape.kv_heads = p->kv_heads;
+    shape.head_dim = p->head_dim;
+    shape.group = p->q_heads / p->kv_heads;
+    shape.window = p->window;
+    shape.c = p->sm_scale * kLog2e;
+    shape.sinks = static_cast<const uint16_t*>(p->sinks);
+    const bool sequence = cache->shard.mode == HC_SHARD_SEQUENCE && cache->shard.world > 1;
+    shape.count_sink = (partial_mode && sequence && cache->shard.rank != 0) ? 0 : 1;
+    return shape;
+}
+
+bool needs_q_prepare(const hc_attn_params* p) {
+    return p->io_dtype != HC_BF16 || p->norm_q != 0 || p->rope != nullptr ||
+           p->gate_layout == HC_GATE_INTERLEAVED;
+}
+
+// Rows a position range needs; checks capacity the way KVCache.advance does (KVCache.swift:202-213).
+hc_status check_positions(const hc_kv_cache* cache, const hc_layer_store& L, int first, int tokens,
+                          const hc_attn_params* p) {
+    if (tokens < 0 || first < 0) return fail(HC_INVALID_ARGUMENT, "negative token count or position");
+    if (L.ring == 0 && first + tokens > cache->context_length) {
+        return fail(HC_KV_OVERFLOW, "position " + std::to_string(first + tokens - 1) + " beyond capacity " +
+                                        std::to_string(cache->context_length));
+    }
+    if (L.ring > 0 && tokens > L.ring - L.desc.window) {
+        return fail(HC_KV_OVERFLOW, "a chunk of " + std::to_string(tokens) + " tokens overruns the ring's margin of " +
+                                        std::to_string(L.ring - L.desc.window));
+    }
+    if (p->rope && first + tokens > p->rope->positions) {
+        return fail(HC_DIM_MISMATCH, "rope table is shorter than the positions asked for");
+    }
+    return HC_OK;
+}
+
+void fill_q_job(PrepJob& job, const hc_attn_params* p, const void* q, void* dst) {
+    const int d = p->head_dim;
+    const int mult = p->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
+    job.src = q;
+    job.src_dtype = p->io_dtype;
+    job.heads = p->q_heads;
+    job.token_stride = (long long)p->q_heads * d * mult;
+    job.head_stride = d * mult;
+    job.norm = p->norm_q;
+    job.weight = static_cast<const uint16_t*>(p->q_norm_weight);
+    job.rope = p->rope ? 1 : 0;
+    job.kind = 0;
+    job.dst = dst;
+}
+
+void fill_kv_jobs(PrepArgs& args, int at, const hc_attn_params* p, const void* k, const void* v) {
+    const int d = p->head_dim;
+    PrepJob& jk = args.job[at];
+    jk.src = k;
+    jk.src_dtype = p->io_dtype;
+    jk.heads = p->kv_heads;
+    jk.token_stride = (long long)p->kv_heads * d;
+    jk.head_stride = d;
+    jk.norm = p->norm_k;
+    jk.weight = static_cast<const uint16_t*>(p->k_norm_weight);
+    jk.rope = p->rope ? 1 : 0;
+    jk.kind = 1;
+    jk.dst = nullptr;
+    PrepJob& jv = args.job[at + 1];
+    jv = jk;
+    jv.src = v;
+    jv.norm = p->norm_v;
+    jv.weight = nullptr;
+    jv.rope = 0;
+    jv.kind = 2;
+}
+
+void fill_common(PrepArgs& args, const hc_attn_params* p) {
+    args.head_dim = p->head_dim;
+    args.eps = p->norm_eps;
+    args.cos = p->rope ? p->rope->cos : nullptr;
+    args.sin = p->rope ? p->rope->sin : nullptr;
+    args.table_positions = p->rope ? p->rope->positions : 0;
+}
+
+const unsigned char* offset_rows(const void* base, size_t rows, size_t row_elems, int dtype) {
+    return static_cast<const unsigned char*>(base) + rows * row_elems * dtype_bytes(dtype);
+}
+
+bool use_tensor_path(const hc_attn_params* p, const AttnShape& shape, hc_status* status) {
+    *status = HC_OK;
+    const char* env = std::getenv("HYDRA_CUDA_FORCE_SIMT");
+    if (p->kernel_path == HC_PATH_SIMT || (p->kernel_path == HC_PATH_AUTO && env && env[0] == '1')) return false;
+    const bool ok = tc_supported(shape);
+    if (p->kernel_path == HC_PATH_TENSOR && !ok) {
+        *status = fail(HC_UNSUPPORTED, "the tcgen05 path serves head_dim 64, 128 and 256 only");
+        return false;
+    }
+    return ok;
+}
+
+// The body shared by hc_attention_prefill and hc_attention_prefill_partial.
+hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q,
+                       void* out, int tokens, int first_position, const hc_attn_params* p,
+                       bool partial_mode, cudaStream_t stream) {
+    if (!ctx || !q || !out) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    hc_status st = validate_params(cache, layer, p);
+    if (st != HC_OK) return st;
+    if (seq < 0 || seq >= cache->max_seqs) return fail(HC_INVALID_ARGUMENT, "sequence index out of range");
+    hc_layer_store& L = cache->layers[size_t(layer)];
+    st = check_positions(cache, L, first_position, tokens, p);
+    if (st != HC_OK) return st;
+    if (tokens == 0) return HC_OK;
+
+    const AttnShape shape = shape_of(cache, p, partial_mode);
+    const CacheView view = view_of(cache, L);
+    const bool tensor = use_tensor_path(p, shape, &st);
+    if (st != HC_OK) return st;
+    const int d = p->head_dim;
+    const int mult = p->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
+    const bool prep = needs_q_prepare(p);
+    const int step = prep ? cache->ws.qprep_tokens : tokens;
+
+    for (int start = 0; start < tokens; start += step) {
+        const int count = std::min(step, tokens - start);
+        const unsigned char* q_rows = offset_rows(q, size_t(start), size_t(p->q_heads) * d * mult, p->io_dtype);
+        const uint16_t* q_bf16 = reinterpret_cast<const uint16_t*>(q_rows);
+        if (prep) {
+            PrepArgs args{};
+            fill_common(args, p);
+            fill_q_job(args.job[0], p, q_rows, cache->ws.qprep);
+            args.n_jobs = 1;
+            args.tokens = count;
+            args.first_position = first_position + start;
+            args.batched = 0;
+            args.seq = seq;
+            args.cache = view;
+            st = launch_prepare(ctx, args, stream);
+            if (st != HC_OK) return st;
+            q_bf16 = cache->ws.qprep;
+        }
+        EpilogueArgs ep{};
+        ep.io_dtype = p->io_dtype;
+        ep.write_partial = partial_mode ? 1 : 0;
+        ep.gate_layout = partial_mode ? HC_GATE_NONE : p->gate_layout;
+        if (partial_mode) {
+            ep.out = static_cast<float*>(out) + size_t(start) * p->q_heads * (d + 2);
+        } else {
+            ep.out = const_cast<unsigned char*>(offset_rows(out, size_t(start), size_t(p->q_heads) * d, p->io_dtype));
+        }
+        if (ep.gate_layout == HC_GATE_SEPARATE) {
+            ep.gate = offset_rows(p->gate, size_t(start), size_t(p->q_heads) * d, p->io_dtype);
+        } else if (ep.gate_layout == HC_GATE_INTERLEAVED) {
+            ep.gate = q_rows;
+        }
+        if (tensor) {
+            st = tc_prefill(ctx, shape, L, view, seq, q_bf16, count, first_position + start, ep, stream);
+        } else {
+            st = simt_prefill(ctx, shape, view, seq, q_bf16, count, first_position + start, ep, stream);
+        }
+        if (st != HC_OK) return st;
+    }
+    return HC_OK;
+}
+
+hc_status decode_impl(hc_context* ctx, hc_kv_cache* cache, int layer, const int* seq_ids,
+                      const int* positions, int n_seq, const void* q, void* out,
+                      const hc_attn_params* p, bool partial_mode, cudaStream_t stream) {
+    if (!ctx || !q || !out || !seq_ids || !positions) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    hc_status st = validate_params(cache, layer, p);
+    if (st != HC_OK) return st;
+    if (n_seq < 0) return fail(HC_INVALID_ARGUMENT, "negative sequence count");
+    hc_layer_store& L = cache->layers[size_t(layer)];
+    for (int b = 0; b < n_seq; ++b) {
+        if (seq_ids[b] < 0 || seq_ids[b] >= cache->max_seqs) return fail(HC_INVALID_ARGUMENT, "sequence index out of range");
+        st = check_positions(cache, L, positions[b], 1, p);
+        if (st != HC_OK) return st;
+    }
+    const AttnShape shape = shape_of(cache, p, partial_mode);
+    const CacheView view = view_of(cache, L);
+    const int d = p->head_dim;
+    const int mult = p->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
+    const bool prep = needs_q_prepare(p);
+
+    for (int start = 0; start < n_seq; start += kMaxBatch) {
+        const int count = std::min(kMaxBatch, n_seq - start);
+        BatchMeta meta{};
+        for (int b = 0; b < count; ++b) {
+            meta.seq[b] = seq_ids[start + b];
+            meta.pos[b] = positions[start + b];
+        }
+        const unsigned char* q_rows = offset_rows(q, size_t(start), size_t(p->q_heads) * d * mult, p->io_dtype);
+        const uint16_t* q_bf16 = reinterpret_cast<const uint16_t*>(q_rows);
+        if (prep) {
+            PrepArgs args{};
+            fill_common(args, p);
+            fill_q_job(args.job[0], p, q_rows, cache->ws.qprep);
+            args.n_jobs = 1;
+            args.tokens = count;
+            args.batched = 1;
+            args.meta = meta;
+            args.cache = view;
+            st = launch_prepare(ctx, args, stream);
+            if (st != HC_OK) return st;
+            q_bf16 = cache->ws.qprep;
+        }
+        EpilogueArgs ep{};
+        ep.io_dtype = p->io_dtype;
+        ep.write_partial = partial_mode ? 1 : 0;
+        ep.gate_layout = partial_mode ? HC_GATE_NONE : p->gate_layout;
+        if (partial_mode) {
+            ep.out = static_cast<float*>(out) + size_t(start) * p->q_heads * (d + 2);
+        } else {
+            ep.out = const_cast<unsigned char*>(offset_rows(out, size_t(start), size_t(p->q_heads) * d, p->io_dtype));
+        }
+        if (ep.gate_layout == HC_GATE_SEPARATE) {
+            ep.gate = offset_rows(p->gate, size_t(start), size_t(p->q_heads) * d, p->io_dtype);
+        } else if (ep.gate_layout == HC_GATE_INTERLEAVED) {
+            ep.gate = q_rows;
+        }
+        st = simt_decode(ctx, shape, view, meta, count, q_bf16, cache->ws, ep, stream);
+        if (st != HC_OK) return st;
+    }
+    return HC_OK;
+}
+
+}  // namespace
+}  // namespace hc
+
+using namespace hc;
+
+extern "C" {
+
+const char* hc_last_error_string(void) { return g_last_error.c_str(); }
+
+hc_status hc_context_create(int device, hc_context** out) {
+    if (!out) return fail(HC_INVALID_ARGUMENT, "null out pointer");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t err = cudaGetDeviceCount(&count);
+    if (err != cudaSuccess || count == 0) {
+        return fail(HC_CUDA_ERROR, std::string("no CUDA device: ") + cudaGetErrorString(err));
+    }
+    if (device < 0 || device >= count) return fail(HC_INVALID_ARGUMENT, "device index out of range");
+    cudaDeviceProp prop{};
+    err = cudaGetDeviceProperties(&prop, device);
+    if (err != cudaSuccess) return check_cuda(err, "cudaGetDeviceProperties");
+    if (prop.major != 10) {
+        return fail(HC_UNSUPPORTED, "this library holds sm_100a code only; device is compute capability " +
+                                        std::to_string(prop.major) + "." + std::to_string(prop.minor));
+    }
+    err = cudaSetDevice(device);
+    if (err != cudaSuccess) return check_cuda(err, "cudaSetDevice");
+    hc_context* ctx = new (std::nothrow) hc_context();
+    if (!ctx) return fail(HC_ALLOC_FAILED, "out of host memory");
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    err = cudaMalloc(&ctx->status_dev, sizeof(int));
+    if (err == cudaSuccess) err = cudaMemset(ctx->status_dev, 0, sizeof(int));
+    if (err == cudaSuccess) err = cudaMallocHost(&ctx->status_host, sizeof(int));
+    if (err != cudaSuccess) {
+        hc_context_destroy(ctx);
+        return fail(HC_ALLOC_FAILED, std::string("context status word: ") + cudaGetErrorString(err));
+    }
+    *ctx->status_host = 0;
+    *out = ctx;
+    return HC_OK;
+}
+
+void hc_context_destroy(hc_context* ctx) {
+    if (!ctx) return;
+    if (ctx->status_dev) cudaFree(ctx->status_dev);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    delete ctx;
+}
+
+hc_status hc_context_check(hc_context* ctx, void* stream) {
+    if (!ctx) return fail(HC_INVALID_ARGUMENT, "null context");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t err = cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+    if (err != cudaSuccess) return check_cuda(err, "stream synchronise");
+    const int word = *ctx->status_host;
+    if (word != 0) {
+        cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), s);
+        cudaStreamSynchronize(s);
+        return fail(HC_TIMEOUT, "a kernel gave up a bounded wait (status word " + std::to_string(word) + ")");
+    }
+    return HC_OK;
+}
+
+uint64_t hc_context_launch_count(const hc_context* ctx) { return ctx ? ctx->launches : 0; }
+
+// ---- RoPE tables --------------------------------------------------------------------------------
+
+hc_status hc_yarn_inverse_frequencies(int head_dim, double base, int initial_context, double scaling,
+                                      double ntk_alpha, double ntk_beta, double* inv_freq,
+                                      double* concentration) {
+    if (!inv_freq || !concentration || head_dim <= 0 || head_dim % 2) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    const int pairs = head_dim / 2;
+    if (!(scaling > 1.0)) {
+        *concentration = 1.0;
+        for (int i = 0; i < pairs; ++i) inv_freq[i] = 1.0 / std::pow(base, double(2 * i) / double(head_dim));
+        return HC_OK;
+    }
+    *concentration = 0.1 * std::log(scaling) + 1.0;
+    const double half_dim = double(head_dim) / 2.0;
+    const double two_pi = 2.0 * 3.14159265358979323846;
+    const double low = half_dim * std::log(double(initial_context) / (ntk_beta * two_pi)) / std::log(base);
+    const double high = half_dim * std::log(double(initial_context) / (ntk_alpha * two_pi)) / std::log(base);
+    if (!(low > 0 && low < high && high < half_dim - 1)) return fail(HC_INVALID_ARGUMENT, "inconsistent YaRN bounds");
+    for (int i = 0; i < pairs; ++i) {
+        const double frequency = std::pow(base, double(2 * i) / double(head_dim));
+        const double ramp = (double(i) - low) / (high - low);
+        const double mask = 1.0 - std::min(std::max(ramp, 0.0), 1.0);
+        inv_freq[i] = (1.0 / (scaling * frequency)) * (1.0 - mask) + (1.0 / frequency) * mask;
+    }
+    return HC_OK;
+}
+
+hc_status hc_inverse_frequencies(int head_dim, double theta, int rotating_pairs, double* inv_freq) {
+    if (!inv_freq || head_dim <= 0 || head_dim % 2) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    const int pairs = head_dim / 2;
+    const int rotating = std::min(std::max(rotating_pairs, 0), pairs);
+    for (int i = 0; i < pairs; ++i) {
+        inv_freq[i] = i < rotating ? 1.0 / std::pow(theta, 2.0 * double(i) / double(head_dim)) : 0.0;
+    }
+    return HC_OK;
+}
+
+hc_status hc_rope_table_create(hc_context* ctx, const double* inv_freq, int pairs, double concentration,
+                               int positions, hc_rope_table** out) {
+    if (!ctx || !inv_freq || !out || pairs <= 0 || positions <= 0) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    *out = nullptr;
+    const size_t count = size_t(positions) * pairs;
+    std::vector<float> host_cos(count), host_sin(count);
+    for (int p = 0; p < positions; ++p) {
+        const double t = double(p);
+        for (int i = 0; i < pairs; ++i) {
+            host_cos[size_t(p) * pairs + i] = float(std::cos(t * inv_freq[i]) * concentration);
+            host_sin[size_t(p) * pairs + i] = float(std::sin(t * inv_freq[i]) * concentration);
+        }
+    }
+    hc_rope_table* table = new (std::nothrow) hc_rope_table();
+    if (!table) return fail(HC_ALLOC_FAILED, "out of host memory");
+    table->device = ctx->device;
+    table->positions = positions;
+    table->pairs = pairs;
+    cudaError_t err = cudaSetDevice(ctx->device);
+    if (err == cudaSuccess) err = cudaMalloc(&table->cos, count * sizeof(float));
+    if (err == cudaSuccess) err = cudaMalloc(&table->sin, count * sizeof(float));
+    if (err == cudaSuccess) err = cudaMemcpy(table->cos, host_cos.data(), count * sizeof(float), cudaMemcpyHostToDevice);
+    if (err == cudaSuccess) err = cudaMemcpy(table->sin, host_sin.data(), count * sizeof(float), cudaMemcpyHostToDevice);
+    if (err != cudaSuccess) {
+        hc_rope_table_destroy(table);
+        return fail(HC_ALLOC_FAILED, std::string("rope table: ") + cudaGetErrorString(err));
+    }
+    *out = table;
+    return HC_OK;
+}
+
+void hc_rope_table_destroy(hc_rope_table* table) {
+    if (!table) return;
+    if (table->cos) cudaFree(table->cos);
+    if (table->sin) cudaFree(table->sin);
+    delete table;
+}
+
+hc_status hc_rope_table_pointers(const hc_rope_table* table, const float** cos_out, const float** sin_out,
+                                 int* positions, int* pairs) {
+    if (!table) return fail(HC_INVALID_ARGUMENT, "null table");
+    if (cos_out) *cos_out = table->cos;
+    if (sin_out) *sin_out = table->sin;
+    if (positions) *positions = table->positions;
+    if (pairs) *pairs = table->pairs;
+    return HC_OK;
+}
+
+// ---- KV cache -----------------------------------------------------------------------------------
+
+hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n_layers, int context_length,
+                             int prefill_chunk, int max_seqs, const hc_shard_desc* shard, hc_kv_cache** out) {
+    if (!ctx || !layers || !out || n_layers <= 0 || context_length <= 0 || prefill_chunk <= 0 || max_seqs <= 0) {
+        return fail(HC_INVALID_ARGUMENT, "bad arguments to hc_kv_cache_create");
+    }
+    *out = nullptr;
+    hc_shard_desc sd{HC_SHARD_NONE, 0, 1};
+    if (shard) {
+        sd = *shard;
+        if (sd.world < 1 || sd.rank < 0 || sd.rank >= sd.world || sd.mode < HC_SHARD_NONE || sd.mode > HC_SHARD_SEQUENCE) {
+            return fail(HC_COMM_ERROR, "inconsistent shard description (mode, rank, world)");
+        }
+        if (sd.world == 1) sd.mode = HC_SHARD_NONE;
+    }
+    const bool sequence = sd.mode == HC_SHARD_SEQUENCE;
+    cudaError_t err = cudaSetDevice(ctx->device);
+    if (err != cudaSuccess) return check_cuda(err, "cudaSetDevice");
+
+    hc_kv_cache* cache = new (std::nothrow) hc_kv_cache();
+    if (!cache) return fail(HC_ALLOC_FAILED, "out of host memory");
+    cache->ctx = ctx;
+    cache->context_length = context_length;
+    cache->prefill_chunk = prefill_chunk;
+    cache->max_seqs = max_seqs;
+    cache->shard = sd;
+    cache->lengths.assign(size_t(max_seqs), 0);
+    cache->layers.resize(size_t(n_layers));
+
+    size_t max_q_elems = 0, max_kv_elems = 0, part_o_floats = 0, part_ml_floats = 0;
+    hc_status st = HC_OK;
+    for (int i = 0; i < n_layers && st == HC_OK; ++i) {
+        hc_layer_store& L = cache->layers[size_t(i)];
+        L.desc = layers[i];
+        if (L.desc.kv_heads == 0) {           // recurrent layer: an index and no memory
+            L.keeps_history = false;
+            continue;
+        }
+        const int d = L.desc.head_dim;
+        if (d <= 0 || d % 8 != 0 || d > 512) {
+            st = fail(HC_DIM_MISMATCH, "head_dim " + std::to_string(d) + " must be a multiple of 8 and at most 512");
+            break;
+        }
+        if (L.desc.kv_heads < 0 || L.desc.q_heads <= 0 || L.desc.q_heads % L.desc.kv_heads != 0 ||
+            !group_ok(L.desc.q_heads / L.desc.kv_heads) || L.desc.window < 0) {
+            st = fail(HC_DIM_MISMATCH, "layer " + std::to_string(i) + ": bad head counts or window");
+            break;
+        }
+        L.keeps_history = true;
+        const bool windowed = L.desc.window > 0;
+        bool ring = false;
+        if (L.desc.storage == HC_STORAGE_AUTO) ring = windowed && context_length > kLinearWindowLimit;
+        else if (L.desc.storage == HC_STORAGE_RING) {
+            if (!windowed) { st = fail(HC_UNSUPPORTED, "ring storage asked for a full-attention layer"); break; }
+            ring = true;
+        } else if (L.desc.storage != HC_STORAGE_LINEAR) { st = fail(HC_INVALID_ARGUMENT, "unknown storage"); break; }
+        if (ring && sequence) { st = fail(HC_UNSUPPORTED, "ring storage cannot be sequence-sharded"); break; }
+        L.ring = ring ? round_up(L.desc.window + prefill_chunk, kTileKeys) : 0;
+        int tiles = (context_length + kTileKeys - 1) / kTileKeys;
+        if (sequence) tiles = (tiles + sd.world - 1) / sd.world;
+        L.capacity = ring ? L.ring : tiles * kTileKeys;
+        const size_t bytes = size_t(max_seqs) * L.desc.kv_heads * L.capacity * d * 2;
+        err = cudaMalloc(&L.k, bytes);
+        if (err == cudaSuccess) err = cudaMalloc(&L.v, bytes);
+        if (err == cudaSuccess) err = cudaMemset(L.k, 0, bytes);
+        if (err == cudaSuccess) err = cudaMemset(L.v, 0, bytes);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            st = fail(HC_ALLOC_FAILED, "KV cache: cannot allocate " + std::to_string(2 * bytes) + " B for layer " + std::to_string(i));
+            break;
+        }
+        max_q_elems = std::max(max_q_elems, size_t(L.desc.q_heads) * d);
+        max_kv_elems = std::max(max_kv_elems, size_t(L.desc.kv_heads) * d);
+        // Split-attention workspace: one partial per (sequence of a launch, query head, visible tile).
+        int visible_tiles = windowed ? L.desc.window / kTileKeys + 2 : (context_length + kTileKeys - 1) / kTileKeys;
+        if (sequence) visible_tiles = (visible_tiles + sd.world - 1) / sd.world + 1;
+        const size_t rows = size_t(std::min(max_seqs, kMaxBatch)) * L.desc.q_heads;
+        part_o_floats = std::max(part_o_floats, rows * visible_tiles * d);
+        part_ml_floats = std::max(part_ml_floats, rows * visible_tiles * 2);
+        st = tc_make_tensor_maps(cache, L);
+    }
+    if (st == HC_OK && max_q_elems == 0) st = fail(HC_UNSUPPORTED, "no layer keeps a key/value history");
+    if (st == HC_OK) {
+        hc::Workspace& ws = cache->ws;
+        ws.qprep_tokens = std::max(std::max(prefill_chunk, std::min(max_seqs, kMaxBatch)), 1);
+        ws.part_o_floats = part_o_floats;
+        ws.part_ml_floats = part_ml_floats;
+        err = cudaMalloc(&ws.qprep, size_t(ws.qprep_tokens) * max_q_elems * 2);
+        if (err == cudaSuccess) err = cudaMalloc(&ws.part_o, part_o_floats * sizeof(float));
+        if (err == cudaSuccess) err = cudaMalloc(&ws.part_ml, part_ml_floats * sizeof(float));
+        // Staging for hc_layer_step_host: q (twice as wide when the gate is interleaved), gate, out, k, v.
+        cache->stage_bytes = size_t(ws.qprep_tokens) * (4 * max_q_elems + 2 * max_kv_elems) * 4;
+        if (err == cudaSuccess) err = cudaMalloc(&cache->stage_dev, cache->stage_bytes);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            st = fail(HC_ALLOC_FAILED, std::string("KV cache workspace: ") + cudaGetErrorString(err));
+        }
+    }
+    if (st != HC_OK) {
+        const std::string message = g_last_error;
+        hc_kv_cache_destroy(cache);
+        g_last_error = message;
+        return st;
+    }
+    *out = cache;
+    return HC_OK;
+}
+
+void hc_kv_cache_destroy(hc_kv_cache* cache) {
+    if (!cache) return;
+    for (hc_layer_store& L : cache->layers) {
+        if (L.k) cudaFree(L.k);
+        if (L.v) cudaFree(L.v);
+        tc_free_tensor_maps(L);
+    }
+    if (cache->ws.qprep) cudaFree(cache->ws.qprep);
+    if (cache->ws.part_o) cudaFree(cache->ws.part_o);
+    if (cache->ws.part_ml) cudaFree(cache->ws.part_ml);
+    if (cache->stage_dev) cudaFree(cache->stage_dev);
+    delete cache;
+}
+
+size_t hc_kv_cache_bytes(const hc_kv_cache* cache) {
+    if (!cache) return 0;
+    size_t total = 0;
+    for (const hc_layer_store& L : cache->layers) {
+        if (L.keeps_history) total += 2 * size_t(cache->max_seqs) * L.desc.kv_heads * L.capacity * L.desc.head_dim * 2;
+    }
+    return total;
+}
+
+hc_status hc_kv_layer_info(const hc_kv_cache* cache, int layer, hc_layer_info* out) {
+    if (!cache || !out || layer < 0 || layer >= int(cache->layers.size())) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    const hc_layer_store& L = cache->layers[size_t(layer)];
+    out->keys = L.k;
+    out->values = L.v;
+    out->ring_size = L.ring;
+    out->capacity = L.capacity;
+    out->entry_bytes = L.keeps_history ? L.desc.kv_heads * L.desc.head_dim * 2 : 0;
+    out->windowed = L.desc.window > 0 ? 1 : 0;
+    out->keeps_history = L.keeps_history ? 1 : 0;
+    return HC_OK;
+}
+
+hc_status hc_kv_read(hc_context* ctx, const hc_kv_cache* cache, int layer, int seq, int position, int tokens,
+                     uint16_t* keys_out, uint16_t* values_out) {
+    if (!ctx || !cache || layer < 0 || layer >= int(cache->layers.size()) || seq < 0 || seq >= cache->max_seqs ||
+        position < 0 || tokens < 0) {
+        return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    }
+    const hc_layer_store& L = cache->layers[size_t(layer)];
+    if (!L.keeps_history) return fail(HC_UNSUPPORTED, "a recurrent layer keeps no rows");
+    if (L.ring == 0 && position + tokens > cache->context_length) return fail(HC_KV_OVERFLOW, "rows beyond capacity");
+    cudaError_t err = cudaDeviceSynchronize();
+    if (err != cudaSuccess) return check_cuda(err, "synchronise before reading the cache");
+    const CacheView view = view_of(cache, L);
+    const int d = L.desc.head_dim, heads = L.desc.kv_heads;
+    for (int t = 0; t < tokens; ++t) {
+        const int pos = position + t;
+        for (int h = 0; h < heads; ++h) {
+            const size_t dst = (size_t(t) * heads + h) * d;
+            if (!row_is_local(view.map, pos)) {
+                if (keys_out) std::memset(keys_out + dst, 0, size_t(d) * 2);
+                if (values_out) std::memset(values_out + dst, 0, size_t(d) * 2);
+                continue;
+            }
+            const size_t src = ((size_t(seq) * heads + h) * L.capacity + row_of_position(view.map, pos)) * d;
+            if (keys_out) err = cudaMemcpy(keys_out + dst, L.k + src, size_t(d) * 2, cudaMemcpyDeviceToHost);
+            if (err == cudaSuccess && values_out) err = cudaMemcpy(values_out + dst, L.v + src, size_t(d) * 2, cudaMemcpyDeviceToHost);
+            if (err != cudaSuccess) return check_cuda(err, "reading the cache");
+        }
+    }
+    return HC_OK;
+}
+
+int hc_shard_owner(int world, int position) {
+    return world <= 1 ? 0 : (position / kTileKeys) % world;
+}
+
+int hc_shard_local_row(int world, int position) {
+    RowMap map{0, 0, world};
+    return row_of_position(map, position);
+}
+
+hc_status hc_kv_visible_range(const hc_kv_cache* cache, int layer, int position, int* start, int* count) {
+    if (!cache || !start || !count || layer < 0 || layer >= int(cache->layers.size()) || position < 0) {
+        return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    }
+    const hc_layer_store& L = cache->layers[size_t(layer)];
+    if (!L.keeps_history) return fail(HC_UNSUPPORTED, "a recurrent layer has no visible range");
+    if (L.desc.window == 0) {
+        *start = 0;
+        *count = position + 1;
+        return HC_OK;
+    }
+    *start = std::max(0, position - L.desc.window + 1);
+    *count = position - *start + 1;
+    return HC_OK;
+}
+
+static bool seq_ok(const hc_kv_cache* cache, int seq) { return cache && seq >= 0 && seq < cache->max_seqs; }
+
+hc_status hc_kv_length(const hc_kv_cache* cache, int seq, int* length) {
+    if (!seq_ok(cache, seq) || !length) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    *length = cache->lengths[size_t(seq)];
+    return HC_OK;
+}
+
+hc_status hc_kv_advance(hc_kv_cache* cache, int seq, int tokens) {
+    if (!seq_ok(cache, seq) || tokens < 0) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    const int length = cache->lengths[size_t(seq)] + tokens;
+    // Only linear layers can overflow (KVCache.swift:204-212).
+    for (const hc_layer_store& L : cache->layers) {
+        if (L.keeps_history && L.ring == 0 && length > cache->context_length) {
+            return fail(HC_KV_OVERFLOW, "position " + std::to_string(length - 1) + " beyond capacity " +
+                                            std::to_string(cache->context_length));
+        }
+    }
+    cache->lengths[size_t(seq)] = length;
+    return HC_OK;
+}
+
+hc_status hc_kv_reset(hc_kv_cache* cache, int seq) {
+    if (!seq_ok(cache, seq)) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    cache->lengths[size_t(seq)] = 0;
+    return HC_OK;
+}
+
+hc_status hc_kv_rewind_floor(const hc_kv_cache* cache, int seq, int* floor) {
+    if (!seq_ok(cache, seq) || !floor) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    // KVCache.rewindFloor (KVCache.swift:95-99): the smallest ring's margin beyond its window.
+    int margin = -1;
+    for (const hc_layer_store& L : cache->layers) {
+        if (L.keeps_history && L.ring > 0) {
+            const int m = L.ring - L.desc.window;
+            margin = margin < 0 ? m : std::min(margin, m);
+        }
+    }
+    *floor = margin < 0 ? 0 : std::max(0, cache->lengths[size_t(seq)] - margin);
+    return HC_OK;
+}
+
+int hc_kv_can_rewind(const hc_kv_cache* cache, int seq, int tokens) {
+    int floor = 0;
+    if (hc_kv_rewind_floor(cache, seq, &floor) != HC_OK) return 0;
+    return tokens >= 0 && tokens <= cache->lengths[size_t(seq)] && tokens >= floor;
+}
+
+hc_status hc_kv_rewind(hc_kv_cache* cache, int seq, int tokens) {
+    if (!seq_ok(cache, seq)) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    if (!hc_kv_can_rewind(cache, seq, tokens)) {
+        int floor = 0;
+        hc_kv_rewind_floor(cache, seq, &floor);
+        return fail(HC_BAD_REWIND, "rewind to " + std::to_string(tokens) + " is outside the history a ring still holds (length " +
+                                       std::to_string(cache->lengths[size_t(seq)]) + ", floor " + std::to_string(floor) + ")");
+    }
+    cache->lengths[size_t(seq)] = tokens;
+    return HC_OK;
+}
+
+// ---- the kernel protocol --------------------------------------------------------------------------
+
+hc_status hc_kv_append(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* k, const void* v,
+                       int tokens, int first_position, const hc_attn_params* params, void* stream) {
+    if (!ctx || !k || !v) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    hc_status st = validate_params(cache, layer, params);
+    if (st != HC_OK) return st;
+    if (!seq_ok(cache, seq)) return fail(HC_INVALID_ARGUMENT, "sequence index out of range");
+    hc_layer_store& L = cache->layers[size_t(layer)];
+    st = check_positions(cache, L, first_position, tokens, params);
+    if (st != HC_OK) return st;
+    const size_t row = size_t(params->kv_heads) * params->head_dim;
+    for (int start = 0; start < tokens; start += 32768) {
+        const int count = std::min(32768, tokens - start);
+        PrepArgs args{};
+        fill_common(args, params);
+        fill_kv_jobs(args, 0, params, offset_rows(k, size_t(start), row, params->io_dtype),
+                     offset_rows(v, size_t(start), row, params->io_dtype));
+        args.n_jobs = 2;
+        args.tokens = count;
+        args.first_position = first_position + start;
+        args.batched = 0;
+        args.seq = seq;
+        args.cache = view_of(cache, L);
+        st = launch_prepare(ctx, args, static_cast<cudaStream_t>(stream));
+        if (st != HC_OK) return st;
+    }
+    return HC_OK;
+}
+
+hc_status hc_kv_append_batch(hc_context* ctx, hc_kv_cache* cache, int layer, const int* seq_ids,
+                             const int* positions, int n_seq, const void* k, const void* v,
+                             const hc_attn_params* params, void* stream) {
+    if (!ctx || !k || !v || !seq_ids || !positions) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    hc_status st = validate_params(cache, layer, params);
+    if (st != HC_OK) return st;
+    hc_layer_store& L = cache->layers[size_t(layer)];
+    const size_t row = size_t(params->kv_heads) * params->head_dim;
+    for (int start = 0; start < n_seq; start += kMaxBatch) {
+        const int count = std::min(kMaxBatch, n_seq - start);
+        PrepArgs args{};
+        fill_common(args, params);
+        fill_kv_jobs(args, 0, params, offset_rows(k, size_t(start), row, params->io_dtype),
+                     offset_rows(v, size_t(start), row, params->io_dtype));
+        args.n_jobs = 2;
+        args.tokens = count;
+        args.batched = 1;
+        for (int b = 0; b < count; ++b) {
+            if (!seq_ok(cache, seq_ids[start + b])) return fail(HC_INVALID_ARGUMENT, "sequence index out of range");
+            st = check_positions(cache, L, positions[start + b], 1, params);
+            if (st != HC_OK) return st;
+            args.meta.seq[b] = seq_ids[start + b];
+            args.meta.pos[b] = positions[start + b];
+        }
+        args.cache = view_of(cache, L);
+        st = launch_prepare(ctx, args, static_cast<cudaStream_t>(stream));
+        if (st != HC_OK) return st;
+    }
+    return HC_OK;
+}
+
+hc_status hc_attention_prefill(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q, void* out,
+                               int tokens, int first_position, const hc_attn_params* params, void* stream) {
+    return prefill_impl(ctx, cache, layer, seq, q, out, tokens, first_position, params, false,
+                        static_cast<cudaStream_t>(stream));
+}
+
+hc_status hc_attention_decode(hc_context* ctx, hc_kv_cache* cache, int layer, const int* seq_ids,
+                              const int* positions, int n_seq, const void* q, void* out,
+                              const hc_attn_params* params, void* stream) {
+    return decode_impl(ctx, cache, layer, seq_ids, positions, n_seq, q, out, params, false,
+                       static_cast<cudaStream_t>(stream));
+}
+
+size_t hc_attention_partial_bytes(const hc_attn_params* params, int rows) {
+    if (!params || rows < 0) return 0;
+    return size_t(rows) * params->q_heads * (params->head_dim + 2) * sizeof(float);
+}
+
+hc_status hc_attention_prefill_partial(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q,
+                                       void* partial, int tokens, int first_position,
+                                       const hc_attn_params* params, void* stream) {
+    return prefill_impl(ctx, cache, layer, seq, q, partial, tokens, first_position, params, true,
+                        static_cast<cudaStream_t>(stream));
+}
+
+hc_status hc_attention_decode_partial(hc_context* ctx, hc_kv_cache* cache, int layer, const int* seq_ids,
+                                      const int* positions, int n_seq, const void* q, void* partial,
+                                      const hc_attn_params* params, void* stream) {
+    return decode_impl(ctx, cache, layer, seq_ids, positions, n_seq, q, partial, params, true,
+                       static_cast<cudaStream_t>(stream));
+}
+
+hc_status hc_attention_combine(hc_context* ctx, const void* gathered, int world, int rows, const void* q, void* out,
+                               const hc_attn_params* params, void* stream) {
+    if (!ctx || !gathered || !out || !params) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    if (world < 1 || rows < 0) return fail(HC_COMM_ERROR, "combine: world must be at least 1");
+    EpilogueArgs ep{};
+    ep.out = out;
+    ep.io_dtype = params->io_dtype;
+    ep.write_partial = 0;
+    ep.gate_layout = params->gate_layout;
+    if (params->gate_layout == HC_GATE_SEPARATE) {
+        if (!params->gate) return fail(HC_INVALID_ARGUMENT, "HC_GATE_SEPARATE without a gate buffer");
+        ep.gate = params->gate;
+    } else if (params->gate_layout == HC_GATE_INTERLEAVED) {
+        if (!q) return fail(HC_INVALID_ARGUMENT, "HC_GATE_INTERLEAVED needs q (the gate sits beside the query)");
+        ep.gate = q;
+    }
+    return launch_combine(ctx, static_cast<const float*>(gathered), world, rows, params->q_heads,
+                          params->head_dim, ep, static_cast<cudaStream_t>(stream));
+}
+
+hc_status hc_rms_norm_heads(hc_context* ctx, void* vector, const void* weight_bf16, int tokens, int heads,
+                            int head_dim, float eps, int io_dtype, void* stream) {
+    if (!ctx || !vector || tokens < 0 || heads <= 0) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    if (head_dim <= 0 || head_dim % 2 != 0 || head_dim > 512) return fail(HC_DIM_MISMATCH, "head_dim must be even and at most 512");
+    for (int start = 0; start < tokens; start += 32768) {
+        PrepArgs args{};
+        args.head_dim = head_dim;
+        args.eps = eps;
+        PrepJob& job = args.job[0];
+        job.src = offset_rows(vector, size_t(start), size_t(heads) * head_dim, io_dtype);
+        job.dst = const_cast<void*>(job.src);
+        job.src_dtype = io_dtype;
+        job.heads = heads;
+        job.token_stride = (long long)heads * head_dim;
+        job.head_stride = head_dim;
+        job.norm = weight_bf16 ? 1 : 2;
+        job.weight = static_cast<const uint16_t*>(weight_bf16);
+        job.rope = 0;
+        job.kind = 3;
+        args.n_jobs = 1;
+        args.tokens = std::min(32768, tokens - start);
+        hc_status st = launch_prepare(ctx, args, static_cast<cudaStream_t>(stream));
+        if (st != HC_OK) return st;
+    }
+    return HC_OK;
+}
+
+hc_status hc_apply_rope(hc_context* ctx, void* vector, const hc_rope_table* table, int tokens, int heads,
+                        int head_dim, int first_position, int io_dtype, void* stream) {
+    if (!ctx || !vector || !table || tokens < 0 || heads <= 0 || first_position < 0) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    if (head_dim <= 0 || head_dim % 2 != 0 || head_dim > 512 || table->pairs != head_dim / 2) {
+        return fail(HC_DIM_MISMATCH, "rope table pairs != head_dim / 2");
+    }
+    if (first_position + tokens > table->positions) return fail(HC_DIM_MISMATCH, "rope table is shorter than the positions asked for");
+    for (int start = 0; start < tokens; start += 32768) {
+        PrepArgs args{};
+        args.head_dim = head_dim;
+        args.cos = table->cos;
+        args.sin = table->sin;
+        args.table_positions = table->positions;
+        PrepJob& job = args.job[0];
+        job.src = offset_rows(vector, size_t(start), size_t(heads) * head_dim, io_dtype);
+        job.dst = const_cast<void*>(job.src);
+        job.src_dtype = io_dtype;
+        job.heads = heads;
+        job.token_stride = (long long)heads * head_dim;
+        job.head_stride = head_dim;
+        job.norm = 0;
+        job.rope = 1;
+        job.kind = 3;
+        args.n_jobs = 1;
+        args.tokens = std::min(32768, tokens - start);
+        args.first_position = first_position + start;
+        hc_status st = launch_prepare(ctx, args, static_cast<cudaStream_t>(stream));
+        if (st != HC_OK) return st;
+    }
+    return HC_OK;
+}
+
+hc_status hc_qwen_split_query_gate(hc_context* ctx, const void* combined, void* query, void* gate, int tokens,
+                                   int heads, int head_dim, int io_dtype, void* stream) {
+    if (!ctx || !combined || !query || !gate || tokens < 0 || heads <= 0 || head_dim <= 0) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    return launch_split_query_gate(ctx, combined, query, gate, tokens, heads, head_dim, io_dtype,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+hc_status hc_qwen_apply_output_gate(hc_context* ctx, void* output, const void* gate, size_t count, int io_dtype,
+                                    void* stream) {
+    if (!ctx || !output || !gate) return fail(HC_INVALID_ARGUMENT, "bad arguments");
+    return launch_output_gate(ctx, output, gate, count, io_dtype, static_cast<cudaStream_t>(stream));
+}
+
+hc_status hc_layer_step_host(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q, const void* k,
+                             const void* v, void* out, int tokens, int first_position,
+                             const hc_attn_params* params, void* stream) {
+    if (!ctx || !q || !k || !v || !out) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    hc_status st = validate_params(cache, layer, params);
+    if (st != HC_OK) return st;
+    if (tokens <= 0) return fail(HC_INVALID_ARGUMENT, "tokens must be positive");
+    if (tokens > cache->ws.qprep_tokens) {
+        return fail(HC_KV_OVERFLOW, "hc_layer_step_host takes at most " + std::to_string(cache->ws.qprep_tokens) + " tokens per call");
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t eb = dtype_bytes(params->io_dtype);
+    const int d = params->head_dim;
+    const int mult = params->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
+    const size_t q_bytes = size_t(tokens) * params->q_heads * d * mult * eb;
+    const size_t kv_bytes = size_t(tokens) * params->kv_heads * d * eb;
+    const size_t o_bytes = size_t(tokens) * params->q_heads * d * eb;
+    const bool sep_gate = params->gate_layout == HC_GATE_SEPARATE;
+    auto align = [](size_t x) { return (x + 255) & ~size_t(255); };
+    unsigned char* base = static_cast<unsigned char*>(cache->stage_dev);
+    unsigned char* dq = base;
+    unsigned char* dk = dq + align(q_bytes);
+    unsigned char* dv = dk + align(kv_bytes);
+    unsigned char* dg = dv + align(kv_bytes);
+    unsigned char* dout = dg + (sep_gate ? align(o_bytes) : 0);
+    if (size_t(dout - base) + o_bytes > cache->stage_bytes) return fail(HC_KV_OVERFLOW, "staging buffer too small");
+    cudaError_t err = cudaMemcpyAsync(dq, q, q_bytes, cudaMemcpyHostToDevice, s);
+    if (err == cudaSuccess) err = cudaMemcpyAsync(dk, k, kv_bytes, cudaMemcpyHostToDevice, s);
+    if (err == cudaSuccess) err = cudaMemcpyAsync(dv, v, kv_bytes, cudaMemcpyHostToDevice, s);
+    if (err == cudaSuccess && sep_gate) err = cudaMemcpyAsync(dg, params->gate, o_bytes, cudaMemcpyHostToDevice, s);
+    if (err != cudaSuccess) return check_cuda(err, "host to device copy");
+    hc_attn_params local = *params;
+    if (sep_gate) local.gate = dg;
+    st = hc_kv_append(ctx, cache, layer, seq, dk, dv, tokens, first_position, &local, stream);
+    if (st != HC_OK) return st;
+    if (tokens == 1) {
+        const int position = first_position;
+        st = hc_attention_decode(ctx, cache, layer, &seq, &position, 1, dq, dout, &local, stream);
+    } else {
+        st = hc_attention_prefill(ctx, cache, layer, seq, dq, dout, tokens, first_position, &local, stream);
+    }
+    if (st != HC_OK) return st;
+    err = cudaMemcpyAsync(out, dout, o_bytes, cudaMemcpyDeviceToHost, s);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+    if (err != cudaSuccess) return check_cuda(err, "device to host copy");
+    return HC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,115 @@
+// common.cuh — arithmetic shared by every attention kernel in this library.
+//
+// The kernels agree bit for bit with one another only because they all go through the functions in
+// this header: the same exp2, the same rounding of the softmax weights to bf16, the same fold.
+// Every floating-point step uses an explicit round-to-nearest intrinsic so that the compiler cannot
+// contract or reassociate it differently in two kernels.
+//
+// The canonical computation (what "attention of one query row" means here):
+//
+//   keys are cut into tiles of 128 absolute positions: tile j = [128 j, 128 j + 128);
+//   for each tile that holds a visible key, the tile partial is
+//       s_k  = q . K_k                       (fp32 accumulate over bf16 inputs)
+//       m    = max over visible k of s_k
+//       p_k  = bf16( exp2( (s_k - m) * c ) ) for visible k, 0 otherwise;   c = sm_scale * log2(e)
+//       l    = sum_k p_k ,  O = sum_k p_k V_k                              (fp32)
+//       mm   = m * c
+//   the row's result is a left fold over its tiles in ascending order, seeded with the sink:
+//       (M, L, A) = (sink * log2(e), 1, 0)             -- "no sink" is sink = bf16(-1e30)
+//       Mn = max(M, mm); a = exp2(M - Mn); b = exp2(mm - Mn)
+//       L = fma(L, a, l * b);  A = fma(A, a, O * b);  M = Mn
+//       out = A / L, then * sigmoid(gate) when gated.
+//
+// Seeding with the sink is the reference's own construction
+// (Sources/HydraMetal/Shaders/attention.metal:156-165): the sink adds to the denominator only.
+// A tile partial does not depend on which kernel, which chunk or which split produced it, and the
+// fold visits tiles in the same order everywhere, so chunked prefill, token-by-token decode and
+// split decode give the same bits as long as they share the tile-partial routine.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hc {
+
+constexpr int kTileKeys = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+// The reference's "unreachable sink": bf16(-1e30) (Sources/HydraMetal/Gemma4LayerRunner.swift:43-49).
+constexpr uint16_t kNoSinkBits = 0xF14A;  // bf16 nearest to -1e30 (-1.00026e30)
+// Seed of a fold that must not count the sink (ranks > 0 of a sequence-sharded cache).
+constexpr float kEmptyMax = -1.0e30f;
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t bits) {
+    return __uint_as_float(uint32_t(bits) << 16);
+}
+__device__ __forceinline__ uint16_t float_to_bf16_bits(float value) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(value));
+}
+__device__ __forceinline__ float round_to_bf16(float value) {
+    return bf16_bits_to_float(float_to_bf16_bits(value));
+}
+
+// Softmax weight of one logit inside its tile: bf16( exp2( (s - m) * c ) ).
+__device__ __forceinline__ float tile_weight(float s, float m, float c) {
+    return round_to_bf16(ex2(__fmul_rn(__fsub_rn(s, m), c)));
+}
+
+// One step of the fold: the coefficients, then the update of any accumulated quantity.
+__device__ __forceinline__ void fold_coefficients(float M, float mm, float& Mn, float& a, float& b) {
+    Mn = fmaxf(M, mm);
+    a = ex2(__fsub_rn(M, Mn));
+    b = ex2(__fsub_rn(mm, Mn));
+}
+__device__ __forceinline__ float fold_value(float acc, float a, float part, float b) {
+    return __fmaf_rn(acc, a, __fmul_rn(part, b));
+}
+
+__device__ __forceinline__ float sigmoid_gate(float g) {
+    return __fdiv_rn(1.0f, __fadd_rn(1.0f, ex2(__fmul_rn(-g, kLog2e))));
+}
+// The last step of a row: divide by the denominator, then the optional gate.
+__device__ __forceinline__ float finish_value(float A, float L, bool gated, float g) {
+    float out = __fdiv_rn(A, L);
+    if (gated) out = __fmul_rn(out, sigmoid_gate(g));
+    return out;
+}
+
+// Activations are fp32 or bf16; these two read and write one element of either.
+__device__ __forceinline__ float load_io(const void* base, size_t index, int dtype) {
+    return dtype == 0 ? reinterpret_cast<const float*>(base)[index]
+                      : bf16_bits_to_float(reinterpret_cast<const uint16_t*>(base)[index]);
+}
+__device__ __forceinline__ void store_io(void* base, size_t index, int dtype, float value) {
+    if (dtype == 0) reinterpret_cast<float*>(base)[index] = value;
+    else reinterpret_cast<uint16_t*>(base)[index] = float_to_bf16_bits(value);
+}
+
+// Where position `pos` of a sequence lives inside one head's rows of the cache.
+//   ring > 0            : physical = pos % ring                      (ring is a multiple of 128)
+//   world > 1 (sequence): tile j = pos / 128 belongs to rank j % world and is that rank's local
+//                         tile j / world
+struct RowMap {
+    int ring;
+    int rank;
+    int world;
+};
+__host__ __device__ __forceinline__ bool row_is_local(const RowMap& map, int pos) {
+    return map.world <= 1 || ((pos / kTileKeys) % map.world) == map.rank;
+}
+__host__ __device__ __forceinline__ int row_of_position(const RowMap& map, int pos) {
+    if (map.world > 1) return ((pos / kTileKeys) / map.world) * kTileKeys + (pos % kTileKeys);
+    return map.ring > 0 ? pos % map.ring : pos;
+}
+// First physical row of absolute tile j (callers only ask for tiles they own).
+__host__ __device__ __forceinline__ int row_of_tile(const RowMap& map, int tile) {
+    return row_of_position(map, tile * kTileKeys);
+}
+
+}  // namespace hc

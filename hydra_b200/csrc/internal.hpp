@@ -1,0 +1,164 @@
+// internal.hpp — host-side objects behind the opaque handles of hydra_cuda.h, and the launchers
+// each .cu file exports to api.cu.  Nothing here is visible outside the shared library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/hydra_cuda.h"
+#include "common.cuh"
+
+namespace hc {
+
+// At most this many sequences share one decode launch; larger batches are cut into launches.
+constexpr int kMaxBatch = 64;
+
+struct BatchMeta {
+    int seq[kMaxBatch];
+    int pos[kMaxBatch];
+};
+
+// One head's rows of one layer, as the kernels address them.
+struct CacheView {
+    uint16_t* k;       // bf16 [max_seqs][kv_heads][capacity][head_dim]
+    uint16_t* v;
+    int capacity;      // rows per (sequence, head)
+    int kv_heads;
+    RowMap map;
+};
+
+struct AttnShape {
+    int q_heads;
+    int kv_heads;
+    int head_dim;
+    int group;          // q_heads / kv_heads
+    int window;         // 0 = full
+    float c;            // sm_scale * log2(e)
+    const uint16_t* sinks;  // bf16 [q_heads] or null
+    int count_sink;     // 0 on ranks > 0 of a sequence-sharded cache
+};
+
+// What the prologue does to one of q, k, v.
+struct PrepJob {
+    const void* src;
+    int src_dtype;
+    int heads;
+    long long token_stride;  // elements between tokens in src
+    int head_stride;         // elements between heads in src (2 * d for an interleaved gate)
+    int norm;                // 0 none, 1 weighted, 2 weightless
+    const uint16_t* weight;
+    int rope;                // 0 / 1
+    int kind;                // 0: dense bf16 [tokens][heads][d]; 1: K rows; 2: V rows; 3: in place
+    void* dst;
+};
+struct PrepArgs {
+    PrepJob job[3];
+    int n_jobs;
+    int head_dim;
+    float eps;
+    const float* cos;        // fp32 [table_positions][head_dim / 2]
+    const float* sin;
+    int table_positions;
+    int tokens;
+    int first_position;      // position of token 0 when batched == 0
+    int batched;             // 1: token t is sequence meta.seq[t] at position meta.pos[t]
+    int seq;                 // sequence when batched == 0
+    CacheView cache;         // for kinds 1 and 2
+    BatchMeta meta;
+};
+
+struct EpilogueArgs {
+    void* out;               // [rows][q_heads][d] io dtype, or fp32 partial [rows][q_heads][d + 2]
+    int io_dtype;
+    int write_partial;       // 1: write (A, M, L) instead of the finished value
+    int gate_layout;
+    const void* gate;        // HC_GATE_SEPARATE: [rows][q_heads][d]; INTERLEAVED: q_proj output
+};
+
+struct Workspace {
+    uint16_t* qprep = nullptr;   // bf16 [qprep_tokens][q_heads][d]
+    int qprep_tokens = 0;
+    float* part_o = nullptr;     // fp32 [rows][tiles][d], rows and tiles those of the call
+    float* part_ml = nullptr;    // fp32 [rows][tiles][2]
+    size_t part_o_floats = 0;    // capacities
+    size_t part_ml_floats = 0;
+};
+
+}  // namespace hc
+
+struct hc_context {
+    int device = 0;
+    int sm_count = 0;
+    uint64_t launches = 0;
+    int* status_dev = nullptr;    // one word the kernels may set on a bounded-wait timeout
+    int* status_host = nullptr;   // pinned mirror
+};
+
+struct hc_rope_table {
+    int device = 0;
+    float* cos = nullptr;
+    float* sin = nullptr;
+    int positions = 0;
+    int pairs = 0;
+};
+
+struct hc_layer_store {
+    hc_layer_desc desc{};
+    uint16_t* k = nullptr;
+    uint16_t* v = nullptr;
+    int ring = 0;
+    int capacity = 0;
+    bool keeps_history = false;
+    void* tmap_k = nullptr;       // tensor maps of the tcgen05 path (host copies), or null
+    void* tmap_v = nullptr;
+};
+
+struct hc_kv_cache {
+    hc_context* ctx = nullptr;
+    std::vector<hc_layer_store> layers;
+    int context_length = 0;
+    int prefill_chunk = 0;
+    int max_seqs = 0;
+    hc_shard_desc shard{HC_SHARD_NONE, 0, 1};
+    std::vector<int> lengths;
+    hc::Workspace ws;
+    void* stage_host = nullptr;   // pinned, for hc_layer_step_host
+    void* stage_dev = nullptr;
+    size_t stage_bytes = 0;
+};
+
+namespace hc {
+
+// Sets the thread's error message and returns `status`.
+hc_status fail(hc_status status, const std::string& message);
+hc_status check_cuda(cudaError_t err, const char* what);
+
+// prologue.cu
+hc_status launch_prepare(hc_context* ctx, const PrepArgs& args, cudaStream_t stream);
+hc_status launch_split_query_gate(hc_context* ctx, const void* combined, void* query, void* gate,
+                                  int tokens, int heads, int d, int dtype, cudaStream_t stream);
+hc_status launch_output_gate(hc_context* ctx, void* output, const void* gate, size_t count,
+                             int dtype, cudaStream_t stream);
+
+// attn_simt.cu
+hc_status simt_prefill(hc_context* ctx, const AttnShape& shape, const CacheView& cache, int seq,
+                       const uint16_t* q, int tokens, int first_position, const EpilogueArgs& ep,
+                       cudaStream_t stream);
+hc_status simt_decode(hc_context* ctx, const AttnShape& shape, const CacheView& cache,
+                      const BatchMeta& meta, int n_seq, const uint16_t* q, const Workspace& ws,
+                      const EpilogueArgs& ep, cudaStream_t stream);
+hc_status launch_combine(hc_context* ctx, const float* gathered, int world, int rows, int q_heads,
+                         int d, const EpilogueArgs& ep, cudaStream_t stream);
+
+// attn_tc.cu
+bool tc_supported(const AttnShape& shape);
+hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer,
+                     const CacheView& cache, int seq, const uint16_t* q, int tokens,
+                     int first_position, const EpilogueArgs& ep, cudaStream_t stream);
+hc_status tc_make_tensor_maps(hc_kv_cache* cache, hc_layer_store& layer);
+void tc_free_tensor_maps(hc_layer_store& layer);
+
+}  // namespace hc

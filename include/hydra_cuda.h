@@ -1,0 +1,330 @@
+/*
+ * hydra_cuda.h — C ABI of HydraCUDA, the Blackwell (sm_100a) attention + KV-cache backend for Hydra.
+ *
+ * This is the whole boundary between Hydra's layer runners and the CUDA kernels: plain C, plain
+ * pointers and sizes, no C++ or framework types.  Each entry point replaces one method of the
+ * kernel protocol that the reference's Metal backend exposes to its runners; the comment above
+ * each one cites that method (path within the Hydra repository : line).
+ *
+ * Conventions
+ *   - Every call returns an hc_status.  Nothing aborts or traps; hc_last_error_string() gives the
+ *     message of the last failure on the calling thread.
+ *   - Device work is enqueued on the caller's stream (a cudaStream_t passed as void*; NULL is the
+ *     default stream) and is asynchronous, like encoding into a Metal command buffer.  Stream order
+ *     gives the write-then-read guarantee the runners rely on ("append, then attend").
+ *   - One caller thread per context.  No call on the step path allocates device memory: the KV
+ *     cache and the split-attention workspace are sized once at hc_kv_cache_create.
+ *   - Activations (q, k, v, gate, out) are device buffers of `io_dtype` (fp32, as the reference's
+ *     buffers are, or bf16).  The cache is bf16.  Sinks and norm weights are bf16 device pointers
+ *     read in place, as the reference reads them from the mapped checkpoint.  RoPE tables are fp32.
+ *   - Shapes: q/out/gate [tokens][q_heads][head_dim]; k/v [tokens][kv_heads][head_dim].
+ *     head_dim must be a multiple of 8 and at most 512 (the reference's own bound,
+ *     Sources/HydraMetal/Shaders/attention.metal:115); q_heads / kv_heads must be a power of two
+ *     no larger than 16.
+ */
+#ifndef HYDRA_CUDA_H
+#define HYDRA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HC_API __attribute__((visibility("default")))
+
+/* Replaces the Swift error enums KernelError (Sources/HydraMetal/AttentionKernels.swift:20-32),
+ * KVCache.CacheError (Sources/HydraMetal/KVCache.swift:106-122) and MetalContext.ContextError
+ * (Sources/HydraMetal/MetalContext.swift:21-42). */
+typedef enum hc_status {
+    HC_OK = 0,
+    HC_ALLOC_FAILED = 1,     /* CacheError.allocationFailed / KernelError.allocationFailed        */
+    HC_KV_OVERFLOW = 2,      /* CacheError.overflow                                               */
+    HC_DIM_MISMATCH = 3,     /* KernelError.dimensionMismatch, the headDim <= 512 precondition     */
+    HC_UNSUPPORTED = 4,      /* CacheError.unsupportedPattern, or a shape no kernel here serves    */
+    HC_BAD_REWIND = 5,       /* the precondition of KVCache.rewind(to:)                            */
+    HC_CUDA_ERROR = 6,       /* ContextError.commandBufferFailed                                   */
+    HC_COMM_ERROR = 7,       /* a sharded call was given inconsistent rank data                    */
+    HC_TIMEOUT = 8,          /* a bounded device-side wait gave up (see hc_context_check)          */
+    HC_INVALID_ARGUMENT = 9  /* null pointer, negative size, unknown enum value                    */
+} hc_status;
+
+typedef enum hc_dtype { HC_F32 = 0, HC_BF16 = 1 } hc_dtype;
+
+/* How a layer's rows are stored (Sources/HydraMetal/KVCache.swift:160-167). */
+typedef enum hc_storage {
+    HC_STORAGE_AUTO = 0,   /* the reference's rule: ring iff windowed and context > 8192          */
+    HC_STORAGE_LINEAR = 1,
+    HC_STORAGE_RING = 2
+} hc_storage;
+
+/* Which kernel family serves attention.  AUTO is what production runs.  The other values exist so
+ * that a measurement can alternate arms inside one process, as the reference's
+ * HYDRA_NO_SPLIT_ATTENTION toggle does (Sources/HydraMetal/ForwardEncoder.swift:1007-1016). */
+typedef enum hc_kernel_path {
+    HC_PATH_AUTO = 0,
+    HC_PATH_SIMT = 1,      /* CUDA-core kernels: any head_dim <= 512                                */
+    HC_PATH_TENSOR = 2     /* tcgen05 / TMEM / TMA kernels: head_dim 64, 128 or 256                 */
+} hc_kernel_path;
+
+typedef enum hc_gate_layout {
+    HC_GATE_NONE = 0,
+    HC_GATE_SEPARATE = 1,    /* gate is its own [tokens][q_heads][head_dim] buffer                 */
+    HC_GATE_INTERLEAVED = 2  /* q is q_proj's raw output [tokens][q_heads][2*head_dim]: head h's
+                                query then head h's gate (Sources/HydraMetal/Shaders/qwen.metal:188-204) */
+} hc_gate_layout;
+
+typedef struct hc_context hc_context;
+typedef struct hc_kv_cache hc_kv_cache;
+typedef struct hc_rope_table hc_rope_table;
+
+/* One layer's geometry.  Replaces ModelDescriptor.attentionGeometry(atLayer:) +
+ * attentionPattern(atLayer:) as KVCache.init consumes them (Sources/HydraMetal/KVCache.swift:139-157).
+ * kv_heads == 0 marks a recurrent layer: it keeps an index and no memory (KVCache.swift:148-156). */
+typedef struct hc_layer_desc {
+    int q_heads;
+    int kv_heads;
+    int head_dim;
+    int window;      /* 0 = full causal; else the sliding window in tokens                         */
+    int storage;     /* hc_storage                                                                 */
+} hc_layer_desc;
+
+/* How a cache is split across GPUs.  The reference has no counterpart (single device).
+ *   world == 1: no sharding.
+ *   HC_SHARD_HEADS:    the caller gives this rank kv_heads/world heads in hc_layer_desc and the
+ *                      matching query heads; nothing is exchanged inside attention.
+ *   HC_SHARD_SEQUENCE: key tiles of 128 positions are dealt round-robin, tile j to rank j % world.
+ *                      Each rank appends only the rows it owns, attends over them, and the ranks'
+ *                      partial results are combined by hc_attention_combine. */
+typedef enum hc_shard_mode { HC_SHARD_NONE = 0, HC_SHARD_HEADS = 1, HC_SHARD_SEQUENCE = 2 } hc_shard_mode;
+typedef struct hc_shard_desc {
+    int mode;   /* hc_shard_mode */
+    int rank;
+    int world;
+} hc_shard_desc;
+
+/* Everything one attention call needs besides the buffers.  Replaces the scalar arguments of
+ * ForwardEncoder.attention / attentionPrefill / rmsNormHeads / applyRoPE
+ * (Sources/HydraMetal/ForwardEncoder.swift:1107-1115, 590-599, 535-538, 974-979). */
+typedef struct hc_attn_params {
+    int q_heads;
+    int kv_heads;
+    int head_dim;
+    int window;              /* 0 = full causal (must agree with the cache layer's window)         */
+    float sm_scale;          /* 1/sqrt(d) for GPT-OSS and Qwen, 1.0 for Gemma                       */
+    int io_dtype;            /* hc_dtype of q, k, v, gate, out                                      */
+    const void* sinks;       /* bf16 [q_heads] device, or NULL: no sink (the reference passes
+                                bf16(-1e30), Sources/HydraMetal/Gemma4LayerRunner.swift:43-49)      */
+    /* Per-head RMSNorm before the rotation (Sources/HydraMetal/Shaders/gemma.metal:785-821). */
+    int norm_q;              /* 0 = none, 1 = with q_norm_weight, 2 = weightless                    */
+    int norm_k;              /* same with k_norm_weight                                             */
+    int norm_v;              /* 0 = none, 2 = weightless (Gemma's v_norm)                           */
+    const void* q_norm_weight; /* bf16 [head_dim] device                                           */
+    const void* k_norm_weight; /* bf16 [head_dim] device                                           */
+    float norm_eps;
+    /* Rotation of q and k (Sources/HydraMetal/Shaders/attention.metal:48-72).  NULL = none. */
+    const hc_rope_table* rope;
+    /* Sigmoid output gate (Sources/HydraMetal/Shaders/qwen.metal:211-219). */
+    int gate_layout;         /* hc_gate_layout                                                      */
+    const void* gate;        /* device, io_dtype, for HC_GATE_SEPARATE                              */
+    int kernel_path;         /* hc_kernel_path                                                      */
+} hc_attn_params;
+
+/* ---- context -------------------------------------------------------------------------------- */
+
+/* Replaces MetalContext.init (Sources/HydraMetal/MetalContext.swift:44-70): binds a device and
+ * checks that it can run these kernels (compute capability 10.x). */
+HC_API hc_status hc_context_create(int device, hc_context** out);
+HC_API void hc_context_destroy(hc_context* ctx);
+
+/* Replaces the check in MetalContext.wait (Sources/HydraMetal/MetalContext.swift:191-202):
+ * synchronises `stream`, then reports a CUDA error or a device-side status word (HC_TIMEOUT if a
+ * bounded wait inside a kernel gave up) recorded since the last check. */
+HC_API hc_status hc_context_check(hc_context* ctx, void* stream);
+
+/* Message of the last failure on this thread; never NULL. */
+HC_API const char* hc_last_error_string(void);
+
+/* Number of kernels this library has launched through `ctx` since it was created (what
+ * ForwardEncoder.dispatchCounter counts, Sources/HydraMetal/ForwardEncoder.swift:38-68). */
+HC_API uint64_t hc_context_launch_count(const hc_context* ctx);
+
+/* ---- RoPE tables ---------------------------------------------------------------------------- */
+
+/* Replaces RoPETables.write (Sources/HydraCore/RoPETables.swift:98-107) for every position at
+ * once: cos(p * f_i) * concentration and sin(...) computed on the host in double, cast to fp32 and
+ * uploaded as [positions][pairs].  `inv_freq` has head_dim/2 entries; a zero entry is an unrotated
+ * pair (partial rotary).  Prefill and decode read the same table, so they rotate identically. */
+HC_API hc_status hc_rope_table_create(hc_context* ctx, const double* inv_freq, int pairs,
+                                      double concentration, int positions, hc_rope_table** out);
+HC_API void hc_rope_table_destroy(hc_rope_table* table);
+/* Device pointers of the table rows (fp32 [positions][pairs]). */
+HC_API hc_status hc_rope_table_pointers(const hc_rope_table* table, const float** cos_out,
+                                        const float** sin_out, int* positions, int* pairs);
+
+/* Inverse frequencies with the YaRN extension; scaling <= 1 gives plain theta^(-2i/d).
+ * Replaces RoPETables.init (Sources/HydraCore/RoPETables.swift:54-85).  Host only. */
+HC_API hc_status hc_yarn_inverse_frequencies(int head_dim, double base, int initial_context,
+                                             double scaling, double ntk_alpha, double ntk_beta,
+                                             double* inv_freq, double* concentration);
+/* Plain frequencies with a zero tail.  Replaces Gemma4RoPETables.init
+ * (Sources/HydraCore/RoPETables.swift:135-148).  Host only. */
+HC_API hc_status hc_inverse_frequencies(int head_dim, double theta, int rotating_pairs,
+                                        double* inv_freq);
+
+/* ---- KV cache ------------------------------------------------------------------------------- */
+
+/* Replaces KVCache.init(model:contextLength:device:) (Sources/HydraMetal/KVCache.swift:132-182).
+ * Allocates, per layer, K and V as bf16 [max_seqs][kv_heads][capacity][head_dim] (head-major, so
+ * one head's history is contiguous), zero-filled, plus the split-attention workspace.
+ * `prefill_chunk` is KVCache.prefillChunk (512 in the reference): a ring holds
+ * window + prefill_chunk rows, rounded up to a multiple of 128.  `shard` may be NULL. */
+HC_API hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n_layers,
+                                    int context_length, int prefill_chunk, int max_seqs,
+                                    const hc_shard_desc* shard, hc_kv_cache** out);
+HC_API void hc_kv_cache_destroy(hc_kv_cache* cache);
+
+/* Replaces KVCache.byteCount (KVCache.swift:184-187): bytes of K and V actually allocated. */
+HC_API size_t hc_kv_cache_bytes(const hc_kv_cache* cache);
+
+/* Replaces KVCache.Layer's fields (KVCache.swift:41-66). */
+typedef struct hc_layer_info {
+    void* keys;          /* device, bf16 */
+    void* values;
+    int ring_size;       /* 0 for linear storage */
+    int capacity;        /* rows per (sequence, head) */
+    int entry_bytes;     /* bytes one token occupies in keys (or values): kv_heads * head_dim * 2 */
+    int windowed;
+    int keeps_history;
+} hc_layer_info;
+HC_API hc_status hc_kv_layer_info(const hc_kv_cache* cache, int layer, hc_layer_info* out);
+
+/* Copies `tokens` rows starting at `position` of one sequence back to the host, in the reference's
+ * row layout [tokens][kv_heads][head_dim] (bf16 bits), synchronously.  For validation: the reference
+ * keeps its cache in CPU-visible storage for the same purpose (KVCache.swift:170-172).  On a
+ * sequence-sharded cache, rows this rank does not own come back as zeros. */
+HC_API hc_status hc_kv_read(hc_context* ctx, const hc_kv_cache* cache, int layer, int seq,
+                            int position, int tokens, uint16_t* keys_out, uint16_t* values_out);
+
+/* Sequence sharding arithmetic (host only, no counterpart in the reference): the rank that owns
+ * `position` in a world of `world` ranks, and the row it occupies in that rank's storage. */
+HC_API int hc_shard_owner(int world, int position);
+HC_API int hc_shard_local_row(int world, int position);
+
+/* Replaces KVCache.visibleRange(layer:position:) (KVCache.swift:193-200). */
+HC_API hc_status hc_kv_visible_range(const hc_kv_cache* cache, int layer, int position, int* start,
+                                     int* count);
+/* Replace KVCache.length / advance() / reset() / rewindFloor / canRewind(to:) / rewind(to:)
+ * (KVCache.swift:68, 202-213, 215-217, 95-104, 223-229), per sequence. */
+HC_API hc_status hc_kv_length(const hc_kv_cache* cache, int seq, int* length);
+HC_API hc_status hc_kv_advance(hc_kv_cache* cache, int seq, int tokens);
+HC_API hc_status hc_kv_reset(hc_kv_cache* cache, int seq);
+HC_API hc_status hc_kv_rewind_floor(const hc_kv_cache* cache, int seq, int* floor);
+HC_API int hc_kv_can_rewind(const hc_kv_cache* cache, int seq, int tokens);
+HC_API hc_status hc_kv_rewind(hc_kv_cache* cache, int seq, int tokens);
+
+/* ---- the kernel protocol -------------------------------------------------------------------- */
+
+/* Replaces ForwardEncoder.writeKeyValue (Sources/HydraMetal/ForwardEncoder.swift:989-1005, one
+ * token) and BatchEncoder.writeKeyValue (Sources/HydraMetal/BatchEncoder.swift:190-208, a chunk):
+ * token t of k, v goes to position first_position + t (modulo the ring).  When params asks for it,
+ * the per-head norm of k (and weightless norm of v) and the rotation of k are applied first, in
+ * that order, fused into the same kernel; with norm_k = norm_v = 0 and rope = NULL this is the
+ * reference's plain cast-and-store.  Does not move the sequence length: call hc_kv_advance. */
+HC_API hc_status hc_kv_append(hc_context* ctx, hc_kv_cache* cache, int layer, int seq,
+                              const void* k, const void* v, int tokens, int first_position,
+                              const hc_attn_params* params, void* stream);
+
+/* The same for one token of each of n_seq sequences (a batched decode step): row i of k, v goes to
+ * sequence seq_ids[i] at positions[i].  seq_ids and positions are HOST arrays.  The reference runs
+ * one sequence at a time and has no counterpart. */
+HC_API hc_status hc_kv_append_batch(hc_context* ctx, hc_kv_cache* cache, int layer,
+                                    const int* seq_ids, const int* positions, int n_seq,
+                                    const void* k, const void* v, const hc_attn_params* params,
+                                    void* stream);
+
+/* Replaces BatchEncoder.attention (Sources/HydraMetal/BatchEncoder.swift:210-246) and
+ * ForwardEncoder.attentionPrefill (Sources/HydraMetal/ForwardEncoder.swift:590-631): causal
+ * attention of `tokens` queries at positions first_position .. first_position + tokens - 1 over
+ * the cache (the chunk's own keys must have been appended first).  The q norm and rotation asked
+ * for in params are applied to q first; the sigmoid gate is applied last.  Image blocks
+ * (blockEnds) are not supported: text only. */
+HC_API hc_status hc_attention_prefill(hc_context* ctx, hc_kv_cache* cache, int layer, int seq,
+                                      const void* q, void* out, int tokens, int first_position,
+                                      const hc_attn_params* params, void* stream);
+
+/* Replaces ForwardEncoder.attention (Sources/HydraMetal/ForwardEncoder.swift:1107-1165) together
+ * with the split kernel and its merge (ForwardEncoder.swift:1064-1105,
+ * Sources/HydraMetal/Shaders/attention.metal:307-452): one query token per sequence.
+ * seq_ids and positions are HOST arrays of n_seq entries (n_seq = 1 is the reference's case);
+ * q and out are [n_seq][q_heads][head_dim].  positions[i] is the query's own position: its key
+ * must already be in the cache.  The visible range follows hc_kv_visible_range. */
+HC_API hc_status hc_attention_decode(hc_context* ctx, hc_kv_cache* cache, int layer,
+                                     const int* seq_ids, const int* positions, int n_seq,
+                                     const void* q, void* out, const hc_attn_params* params,
+                                     void* stream);
+
+/* Sequence-sharded attention, step 1 of 2 (no counterpart in the reference).  Like
+ * hc_attention_prefill / hc_attention_decode over the key tiles this rank owns, but writes this
+ * rank's unnormalised partial (running maximum, denominator, numerator) instead of the output:
+ * fp32 [rows][q_heads][head_dim + 2] with rows = tokens (prefill) or n_seq (decode), laid out as
+ * head_dim numerators, then the maximum, then the denominator.  The sink is counted by rank 0
+ * only.  The caller all-gathers the ranks' partials (NCCL) into [world][rows][q_heads][head_dim+2]
+ * and every rank calls hc_attention_combine on the gathered buffer. */
+HC_API size_t hc_attention_partial_bytes(const hc_attn_params* params, int rows);
+HC_API hc_status hc_attention_prefill_partial(hc_context* ctx, hc_kv_cache* cache, int layer,
+                                              int seq, const void* q, void* partial, int tokens,
+                                              int first_position, const hc_attn_params* params,
+                                              void* stream);
+HC_API hc_status hc_attention_decode_partial(hc_context* ctx, hc_kv_cache* cache, int layer,
+                                             const int* seq_ids, const int* positions, int n_seq,
+                                             const void* q, void* partial,
+                                             const hc_attn_params* params, void* stream);
+/* Step 2 of 2: folds the `world` partials in rank order (the same log-sum-exp merge as
+ * Sources/HydraMetal/Shaders/attention.metal:418-452), divides, applies the gate, writes `out`.
+ * Every rank computes the same bits.  `q` is only read for HC_GATE_INTERLEAVED (the gate sits
+ * beside the query); pass NULL otherwise. */
+HC_API hc_status hc_attention_combine(hc_context* ctx, const void* gathered, int world, int rows,
+                                      const void* q, void* out, const hc_attn_params* params,
+                                      void* stream);
+
+/* Stand-alone forms of the element-wise kernels, for runners that call them one by one as the
+ * reference does.  In place on `vector` (io_dtype).
+ * hc_rms_norm_heads replaces ForwardEncoder.rmsNormHeads (ForwardEncoder.swift:535-551) and
+ * BatchEncoder.rmsNormHeadsBatch (BatchEncoder.swift:429-446); weight NULL = weightless.
+ * hc_apply_rope replaces ForwardEncoder.applyRoPE / applyRoPEBatched (ForwardEncoder.swift:974-987,
+ * 702-719) and BatchEncoder.applyRoPE (BatchEncoder.swift:175-188): token t uses the table row of
+ * position first_position + t. */
+HC_API hc_status hc_rms_norm_heads(hc_context* ctx, void* vector, const void* weight_bf16,
+                                   int tokens, int heads, int head_dim, float eps, int io_dtype,
+                                   void* stream);
+HC_API hc_status hc_apply_rope(hc_context* ctx, void* vector, const hc_rope_table* table,
+                               int tokens, int heads, int head_dim, int first_position,
+                               int io_dtype, void* stream);
+/* Replaces ForwardEncoder.qwenSplitQueryGate (ForwardEncoder.swift:856-869). */
+HC_API hc_status hc_qwen_split_query_gate(hc_context* ctx, const void* combined, void* query,
+                                          void* gate, int tokens, int heads, int head_dim,
+                                          int io_dtype, void* stream);
+/* Replaces ForwardEncoder.qwenApplyOutputGate (ForwardEncoder.swift:872-882). */
+HC_API hc_status hc_qwen_apply_output_gate(hc_context* ctx, void* output, const void* gate,
+                                           size_t count, int io_dtype, void* stream);
+
+/* ---- host-buffer convenience (what a runner without device buffers of its own calls) --------- */
+
+/* One whole step of the path with HOST buffers: copies q, k, v (and gate) to the device, appends,
+ * attends (prefill if tokens > 1, decode otherwise), copies `out` back and synchronises the stream.
+ * It does not move the sequence length (a model calls it once per layer and hc_kv_advance once per
+ * token).  The copies go through a device staging buffer owned by the cache; they are part of the
+ * call, which takes at most max(prefill_chunk, max_seqs) tokens.  q/k/v/gate/out are host pointers of params->io_dtype; params->gate must be a HOST
+ * pointer here.  Replaces nothing one-to-one: on Apple Silicon the reference's buffers are shared
+ * between CPU and GPU (Sources/HydraMetal/KVCache.swift:170-172), so its runners never copy. */
+HC_API hc_status hc_layer_step_host(hc_context* ctx, hc_kv_cache* cache, int layer, int seq,
+                                    const void* q, const void* k, const void* v, void* out,
+                                    int tokens, int first_position, const hc_attn_params* params,
+                                    void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HYDRA_CUDA_H */
