@@ -40,6 +40,15 @@ def max_abs(actual, expected) -> float:
     return float(np.max(np.abs(np.asarray(actual, np.float64) - np.asarray(expected, np.float64))))
 
 
+def within_tolerance(actual, expected, tol=1e-2, bf16_output=True) -> bool:
+    """The parity bound: |error| <= tol on unit-variance outputs.  When the output buffer itself is
+    bf16 its own rounding (half a bf16 step, 2^-8 relative at worst) is allowed on top."""
+    actual = np.asarray(actual, np.float64)
+    expected = np.asarray(expected, np.float64)
+    bound = tol + (2.0 ** -8) * np.abs(expected) if bf16_output else tol
+    return bool(np.all(np.abs(actual - expected) <= bound))
+
+
 def normal_bf16(rng, shape, scale=1.0) -> np.ndarray:
     return ho.bf16_round((rng.standard_normal(shape) * scale).astype(np.float32))
 
