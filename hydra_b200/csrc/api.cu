@@ -251,6 +251,8 @@ hc_status decode_impl(hc_context* ctx, hc_kv_cache* cache, int layer, const int*
     }
     const AttnShape shape = shape_of(cache, p, partial_mode);
     const CacheView view = view_of(cache, L);
+    const bool tensor = use_tensor_path(p, shape, &st);
+    if (st != HC_OK) return st;
     const int d = p->head_dim;
     const int mult = p->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
     const bool prep = needs_q_prepare(p);
@@ -291,7 +293,8 @@ hc_status decode_impl(hc_context* ctx, hc_kv_cache* cache, int layer, const int*
         } else if (ep.gate_layout == HC_GATE_INTERLEAVED) {
             ep.gate = q_rows;
         }
-        st = simt_decode(ctx, shape, view, meta, count, q_bf16, cache->ws, ep, stream);
+        if (tensor) st = tc_decode(ctx, shape, L, view, meta, count, q_bf16, cache->ws, ep, stream);
+        else st = simt_decode(ctx, shape, view, meta, count, q_bf16, cache->ws, ep, stream);
         if (st != HC_OK) return st;
     }
     return HC_OK;

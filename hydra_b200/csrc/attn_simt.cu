@@ -515,9 +515,15 @@ hc_status simt_decode(hc_context* ctx, const AttnShape& shape, const CacheView& 
     ctx->launches += 1;
     err = cudaGetLastError();
     if (err != cudaSuccess) return check_cuda(err, "decode_tiles_kernel launch");
+    return launch_merge(ctx, shape, meta, n_seq, ws, max_tiles, world, cache.map.rank, ep, stream);
+}
+
+hc_status launch_merge(hc_context* ctx, const AttnShape& shape, const BatchMeta& meta, int n_seq,
+                       const Workspace& ws, int part_tiles, int world, int rank, const EpilogueArgs& ep,
+                       cudaStream_t stream) {
     dim3 mgrid(shape.q_heads, n_seq);
-    merge_tiles_kernel<<<mgrid, kThreads, 0, stream>>>(shape, meta, ws.part_o, ws.part_ml,
-                                                      max_tiles, world, cache.map.rank, ep);
+    merge_tiles_kernel<<<mgrid, kThreads, 0, stream>>>(shape, meta, ws.part_o, ws.part_ml, part_tiles,
+                                                      world, rank, ep);
     ctx->launches += 1;
     return check_cuda(cudaGetLastError(), "merge_tiles_kernel launch");
 }

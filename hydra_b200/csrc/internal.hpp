@@ -150,6 +150,9 @@ hc_status simt_prefill(hc_context* ctx, const AttnShape& shape, const CacheView&
 hc_status simt_decode(hc_context* ctx, const AttnShape& shape, const CacheView& cache,
                       const BatchMeta& meta, int n_seq, const uint16_t* q, const Workspace& ws,
                       const EpilogueArgs& ep, cudaStream_t stream);
+hc_status launch_merge(hc_context* ctx, const AttnShape& shape, const BatchMeta& meta, int n_seq,
+                       const Workspace& ws, int part_tiles, int world, int rank, const EpilogueArgs& ep,
+                       cudaStream_t stream);
 hc_status launch_combine(hc_context* ctx, const float* gathered, int world, int rows, int q_heads,
                          int d, const EpilogueArgs& ep, cudaStream_t stream);
 
@@ -158,6 +161,9 @@ bool tc_supported(const AttnShape& shape);
 hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer,
                      const CacheView& cache, int seq, const uint16_t* q, int tokens,
                      int first_position, const EpilogueArgs& ep, cudaStream_t stream);
+hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer,
+                    const CacheView& cache, const BatchMeta& meta, int n_seq, const uint16_t* q,
+                    const Workspace& ws, const EpilogueArgs& ep, cudaStream_t stream);
 hc_status tc_make_tensor_maps(hc_kv_cache* cache, hc_layer_store& layer);
 void tc_free_tensor_maps(hc_layer_store& layer);
 

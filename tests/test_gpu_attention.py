@@ -433,3 +433,60 @@ def test_layer_step_with_host_buffers(hb, ctx):
     want = ho.attention_rows(q, np.arange(tokens + 1), k, v, 0.125, 0, sinks=sinks)
     assert tl.max_abs(out, want[:tokens]) < TOL and tl.max_abs(one, want[tokens:]) < TOL
     layer.close()
+
+
+# ---- the tcgen05 path -------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("case", [
+    dict(q_heads=8, kv_heads=1, d=64, window=0, tokens=333, chunk=100),
+    dict(q_heads=64, kv_heads=8, d=64, window=128, tokens=700, chunk=512),
+    dict(q_heads=4, kv_heads=4, d=64, window=0, tokens=260, chunk=129),
+    dict(q_heads=32, kv_heads=2, d=64, window=200, tokens=520, chunk=256),
+    dict(q_heads=16, kv_heads=8, d=128, window=0, tokens=300, chunk=128),
+    dict(q_heads=16, kv_heads=2, d=128, window=150, tokens=400, chunk=333),
+])
+def test_tensor_path_prefill_and_decode(hb, ctx, case):
+    """The tcgen05 kernels against the oracle, against the CUDA-core kernels (tolerance) and
+    against themselves (chunked == one-shot == token by token, exactly)."""
+    rng = np.random.default_rng(201)
+    qh, kvh, d, tokens, chunk, window = (case[k] for k in ("q_heads", "kv_heads", "d", "tokens", "chunk", "window"))
+    q = tl.normal_bf16(rng, (tokens, qh, d))
+    k = tl.normal_bf16(rng, (tokens, kvh, d))
+    v = tl.normal_bf16(rng, (tokens, kvh, d))
+    sinks = tl.normal_bf16(rng, (qh,))
+    want = ho.attention_rows(q, np.arange(tokens), k, v, 1 / np.sqrt(d), window, sinks=sinks)
+    outs = {}
+    for path in (hb.capi.HC_PATH_TENSOR, hb.capi.HC_PATH_SIMT):
+        layer = tl.Layer(hb, ctx, qh, kvh, d, 1024, window=window, sinks=sinks, kernel_path=path, prefill_chunk=1024)
+        layer.append(k, v, 0)
+        whole = layer.prefill(q, 0)
+        chunked = np.concatenate([layer.prefill(q[s:s + chunk], s) for s in range(0, tokens, chunk)])
+        steps = [0, 1, 127, 128, 129, tokens // 2, tokens - 1]
+        stepwise = np.concatenate([layer.decode(q[t:t + 1], [t]) for t in steps])
+        assert np.array_equal(whole, chunked), path
+        assert np.array_equal(stepwise, whole[steps]), path
+        assert tl.within_tolerance(whole, want), path
+        outs[path] = whole
+        layer.close()
+    assert tl.max_abs(outs[hb.capi.HC_PATH_TENSOR], outs[hb.capi.HC_PATH_SIMT]) < 2e-2
+
+
+def test_tensor_path_batched_ragged_decode(hb, ctx):
+    rng = np.random.default_rng(211)
+    qh, kvh, d, batch = 64, 8, 64, 5
+    lengths = [130, 1, 700, 257, 1024]
+    q = tl.normal_bf16(rng, (batch, qh, d))
+    sinks = tl.normal_bf16(rng, (qh,))
+    layer = tl.Layer(hb, ctx, qh, kvh, d, 1024, sinks=sinks, max_seqs=batch, kernel_path=hb.capi.HC_PATH_TENSOR,
+                     prefill_chunk=1024)
+    hist = []
+    for seq, n in enumerate(lengths):
+        k = tl.normal_bf16(rng, (n, kvh, d))
+        v = tl.normal_bf16(rng, (n, kvh, d))
+        layer.append(k, v, 0, seq=seq)
+        hist.append((k, v))
+    got = layer.decode(q, [n - 1 for n in lengths], seq_ids=list(range(batch)))
+    for seq, n in enumerate(lengths):
+        want = ho.attention_rows(q[seq:seq + 1], [n - 1], hist[seq][0], hist[seq][1], 0.125, 0, sinks=sinks)
+        assert tl.within_tolerance(got[seq], want[0]), seq
+    layer.close()
