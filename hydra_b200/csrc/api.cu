@@ -610,6 +610,24 @@ hc_status hc_kv_read(hc_context* ctx, const hc_kv_cache* cache, int layer, int s
     if (err != cudaSuccess) return check_cuda(err, "synchronise before reading the cache");
     const CacheView view = view_of(cache, L);
     const int d = L.desc.head_dim, heads = L.desc.kv_heads;
+    if (L.ring == 0 && view.map.world <= 1 && tokens > 0) {
+        // Linear storage: a head's rows are contiguous; one copy per head, then interleave on the host.
+        std::vector<uint16_t> plane(size_t(tokens) * d);
+        for (int which = 0; which < 2; ++which) {
+            uint16_t* out = which == 0 ? keys_out : values_out;
+            if (!out) continue;
+            const uint16_t* base = which == 0 ? L.k : L.v;
+            for (int h = 0; h < heads; ++h) {
+                const size_t src = ((size_t(seq) * heads + h) * L.capacity + position) * d;
+                err = cudaMemcpy(plane.data(), base + src, plane.size() * 2, cudaMemcpyDeviceToHost);
+                if (err != cudaSuccess) return check_cuda(err, "reading the cache");
+                for (int t = 0; t < tokens; ++t) {
+                    std::memcpy(out + (size_t(t) * heads + h) * d, plane.data() + size_t(t) * d, size_t(d) * 2);
+                }
+            }
+        }
+        return HC_OK;
+    }
     for (int t = 0; t < tokens; ++t) {
         const int pos = position + t;
         for (int h = 0; h < heads; ++h) {

@@ -139,12 +139,14 @@ class Layer:
 
 def oracle_path(q, k, v, positions, sm_scale, window=0, sinks=None, gate=None, inv_freq=None,
                 concentration=1.0, q_norm=None, k_norm=None, norm_v=False, eps=1e-6,
-                key_positions=None):
+                key_positions=None, cache_rows=None):
     """The reference path in double precision on the same (bf16-rounded) inputs.
 
     q [n][qh][d] raw queries at `positions`; k, v [history][kvh][d] raw keys/values at positions
     0..history-1.  Norm and rotation are applied as the reference orders them, the results rounded
-    to bf16 as the cache holds them, then attention_rows.
+    to bf16 as the cache holds them, then attention_rows.  `cache_rows=(k, v)` replaces the oracle's
+    own prologue on k, v by rows read back from the device cache, so that the comparison measures
+    attention alone (the reference's rule: the oracle sees the values the kernel sees).
     """
     history = k.shape[0]
     if key_positions is None:
@@ -153,7 +155,27 @@ def oracle_path(q, k, v, positions, sm_scale, window=0, sinks=None, gate=None, i
     if inv_freq is not None:
         kc, ks = ho.rope_tables(inv_freq, key_positions, concentration, as_float32=True)
         qc, qs = ho.rope_tables(inv_freq, positions, concentration, as_float32=True)
-    kp = ho.prepare_heads(k, k_norm, k_norm is not None, eps, kc, ks)
-    vp = ho.prepare_heads(v, None, norm_v, eps, None, None)
+    if cache_rows is not None:
+        kp, vp = cache_rows
+    else:
+        kp = ho.prepare_heads(k, k_norm, k_norm is not None, eps, kc, ks)
+        vp = ho.prepare_heads(v, None, norm_v, eps, None, None)
     qp = ho.prepare_heads(q, q_norm, q_norm is not None, eps, qc, qs)
     return ho.attention_rows(qp, positions, kp, vp, sm_scale, window, sinks=sinks, gate=gate)
+
+
+def read_cache(cache, layer, tokens, kv_heads, head_dim, seq=0, position=0):
+    """The device cache's rows [position, position + tokens) as float32 [tokens][kv_heads][d]."""
+    keys, values = cache.read(layer, position, tokens, seq=seq)
+    return (ho.bf16_decode(keys).reshape(tokens, kv_heads, head_dim),
+            ho.bf16_decode(values).reshape(tokens, kv_heads, head_dim))
+
+
+def prologue_matches(have, want) -> bool:
+    """The cache against the oracle's prologue.  The device normalises and rotates in fp32, the
+    oracle in double; after rounding to bf16 the two may land on neighbouring bf16 values for a
+    small fraction of the elements, never further apart."""
+    have = np.asarray(have, np.float64).reshape(-1)
+    want = np.asarray(want, np.float64).reshape(-1)
+    step = np.abs(have - want) / np.maximum(np.abs(want), 1e-3)
+    return bool(np.max(step) < 2.0 ** -7 and np.mean(have != want) < 0.02)

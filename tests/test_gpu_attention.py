@@ -238,17 +238,15 @@ def test_gemma_block_norms_rotation_scale_one(hb, ctx):
                      k_norm=kn, norm_v=True)
     layer.append(k, v, 0)
     got = layer.prefill(q, 0)
-    want = tl.oracle_path(q, k, v, np.arange(tokens), 1.0, window, inv_freq=inv, q_norm=qn, k_norm=kn, norm_v=True)
-    assert tl.within_tolerance(got, want)
-    # the cache holds what the oracle's prologue produces, up to one bf16 step on rounding ties
-    keys_bits, values_bits = layer.cache.read(0, 0, tokens)
+    # 1. the cache holds what the oracle's prologue produces
+    k_dev, v_dev = tl.read_cache(layer.cache, 0, tokens, kvh, d)
     kc, ks = ho.rope_tables(inv, np.arange(tokens), as_float32=True)
-    k_want = ho.prepare_heads(k, kn, True, 1e-6, kc, ks).reshape(tokens, -1)
-    v_want = ho.prepare_heads(v, None, True, 1e-6).reshape(tokens, -1)
-    for bits, want_rows in ((keys_bits, k_want), (values_bits, v_want)):
-        have = ho.bf16_decode(bits)
-        assert np.max(np.abs(have - want_rows) / np.maximum(np.abs(want_rows), 1e-3)) < 2 ** -7
-        assert np.mean(have != want_rows) < 0.02
+    assert tl.prologue_matches(k_dev, ho.prepare_heads(k, kn, True, 1e-6, kc, ks))
+    assert tl.prologue_matches(v_dev, ho.prepare_heads(v, None, True, 1e-6))
+    # 2. attention over those rows
+    want = tl.oracle_path(q, k, v, np.arange(tokens), 1.0, window, inv_freq=inv, q_norm=qn, k_norm=kn,
+                          norm_v=True, cache_rows=(k_dev, v_dev))
+    assert tl.within_tolerance(got, want)
     layer.close()
 
 
@@ -264,11 +262,16 @@ def test_qwen_block_partial_rotary_interleaved_gate(hb, ctx):
     qn = ho.bf16_round((1 + 0.1 * rng.standard_normal(d)).astype(np.float32))
     kn = ho.bf16_round((1 + 0.1 * rng.standard_normal(d)).astype(np.float32))
     inv = ho.inverse_frequencies(d, 1e7, int(d * 0.25) // 2)
-    want = tl.oracle_path(q, k, v, np.arange(tokens), 1 / 16.0, 0, gate=gate, inv_freq=inv, q_norm=qn, k_norm=kn)
     for layout in ("interleaved", "separate"):
         gl = hb.capi.HC_GATE_INTERLEAVED if layout == "interleaved" else hb.capi.HC_GATE_NONE
         layer = tl.Layer(hb, ctx, qh, kvh, d, 128, rope_inv_freq=inv, q_norm=qn, k_norm=kn, gate_layout=gl)
         layer.append(k, v, 0)
+        k_dev, v_dev = tl.read_cache(layer.cache, 0, tokens, kvh, d)
+        kc, ks = ho.rope_tables(inv, np.arange(tokens), as_float32=True)
+        assert tl.prologue_matches(k_dev, ho.prepare_heads(k, kn, True, 1e-6, kc, ks))
+        assert np.array_equal(v_dev, v)
+        want = tl.oracle_path(q, k, v, np.arange(tokens), 1 / 16.0, 0, gate=gate, inv_freq=inv, q_norm=qn,
+                              k_norm=kn, cache_rows=(k_dev, v_dev))
         if layout == "interleaved":
             got = _prefill_interleaved(layer, combined)
             last = _decode_interleaved(layer, combined[-1:], tokens - 1)

@@ -28,8 +28,10 @@ def ctx(hb):
     c.close()
 
 
-def oracle_rows(cfg, spec, entry, rows, k_hist=None, v_hist=None, positions=None):
-    """The oracle on query rows `rows` of one layer; history defaults to the layer's own k, v."""
+def oracle_rows(cfg, spec, entry, rows, k_hist=None, v_hist=None, positions=None, cache=None, layer=0):
+    """The oracle on query rows `rows` of one layer; history defaults to the layer's own k, v.
+    With `cache`, the keys and values are the rows the device cache holds (checked separately
+    against the oracle's prologue), so the comparison measures attention alone."""
     d = cfg.head_dim
     inv = ho.inverse_frequencies(d, spec.theta, spec.rotating_pairs)
     q = entry["q"][rows]
@@ -40,9 +42,17 @@ def oracle_rows(cfg, spec, entry, rows, k_hist=None, v_hist=None, positions=None
     v = entry["v"] if v_hist is None else v_hist
     positions = np.asarray(rows if positions is None else positions)
     upto = int(positions.max()) + 1
+    cache_rows = None
+    if cache is not None:
+        cache_rows = tl.read_cache(cache, layer, upto, cfg.kv_heads, d)
+        kc, ks = ho.rope_tables(inv, np.arange(upto), as_float32=True)
+        k_norm = entry.get("k_norm")
+        assert tl.prologue_matches(cache_rows[0], ho.prepare_heads(k[:upto], k_norm, k_norm is not None, 1e-6, kc, ks))
+        assert tl.prologue_matches(cache_rows[1], ho.prepare_heads(v[:upto], None, cfg.v_norm, 1e-6))
     return tl.oracle_path(q, k[:upto], v[:upto], positions, cfg.scale, spec.window,
                           sinks=entry.get("sinks"), gate=gate, inv_freq=inv,
-                          q_norm=entry.get("q_norm"), k_norm=entry.get("k_norm"), norm_v=cfg.v_norm)
+                          q_norm=entry.get("q_norm"), k_norm=entry.get("k_norm"), norm_v=cfg.v_norm,
+                          cache_rows=cache_rows)
 
 
 def sample_rows(prompt, chunk, stride):
@@ -137,7 +147,7 @@ def test_c3_gemma_stack(hb, ctx):
     ctx.check()
     rows = np.array([0, 1, 511, 512, 1023, 1024, 1500, 4095, 4096, 8191, 8192, 8195])
     for layer in (0, 5):                                   # one local, the global one
-        want = oracle_rows(cfg, cfg.layers[layer], inputs.layers[layer], rows)
+        want = oracle_rows(cfg, cfg.layers[layer], inputs.layers[layer], rows, cache=run.cache, layer=layer)
         assert tl.within_tolerance(run.output(layer)[rows], want), layer
     run.close()
 
@@ -158,7 +168,8 @@ def test_c4_qwen_gated_decode_at_32768(hb, ctx):
     spec, entry = cfg.layers[0], inputs.layers[0]
     inv = ho.inverse_frequencies(d, spec.theta, spec.rotating_pairs)
     c, s = ho.rope_tables(inv, [position], as_float32=True)
-    k_new = ho.prepare_heads(entry["k"], entry["k_norm"], True, 1e-6, c, s)
+    k_new, _ = tl.read_cache(run.cache, 0, 1, cfg.kv_heads, d, position=position)
+    assert tl.prologue_matches(k_new, ho.prepare_heads(entry["k"], entry["k_norm"], True, 1e-6, c, s))
     q = ho.prepare_heads(np.ascontiguousarray(entry["q"][:, :, :d]), entry["q_norm"], True, 1e-6, c, s)
     gate = np.ascontiguousarray(entry["q"][:, :, d:])
     want = ho.attention_rows(q, [position], np.concatenate([hk, k_new]), np.concatenate([hv, entry["v"]]),
