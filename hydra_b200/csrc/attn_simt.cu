@@ -130,11 +130,11 @@ __device__ void tile_partial(const SimtSmem& sm, const uint16_t* __restrict__ k_
         for (int offset = 16; offset > 0; offset >>= 1) {
             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, offset));
         }
-        const float m_safe = (m == neg_inf) ? 0.0f : m;
-        v0 = tile_weight(v0, m_safe, c);
-        v1 = tile_weight(v1, m_safe, c);
-        v2 = tile_weight(v2, m_safe, c);
-        v3 = tile_weight(v3, m_safe, c);
+        const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, c);
+        v0 = tile_weight(v0, neg_mc, c);
+        v1 = tile_weight(v1, neg_mc, c);
+        v2 = tile_weight(v2, neg_mc, c);
+        v3 = tile_weight(v3, neg_mc, c);
         srow[lane] = v0;
         srow[lane + 32] = v1;
         srow[lane + 64] = v2;

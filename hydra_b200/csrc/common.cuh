@@ -11,7 +11,7 @@
 //   for each tile that holds a visible key, the tile partial is
 //       s_k  = q . K_k                       (fp32 accumulate over bf16 inputs)
 //       m    = max over visible k of s_k
-//       p_k  = bf16( exp2( (s_k - m) * c ) ) for visible k, 0 otherwise;   c = sm_scale * log2(e)
+//       p_k  = bf16( exp2( fma(s_k, c, -(m * c)) ) ) for visible k, 0 otherwise;  c = sm_scale * log2(e)
 //       l    = sum_k p_k ,  O = sum_k p_k V_k                              (fp32)
 //       mm   = m * c
 //   the row's result is a left fold over its tiles in ascending order, seeded with the sink:
@@ -56,9 +56,13 @@ __device__ __forceinline__ float round_to_bf16(float value) {
     return bf16_bits_to_float(float_to_bf16_bits(value));
 }
 
-// Softmax weight of one logit inside its tile: bf16( exp2( (s - m) * c ) ).
-__device__ __forceinline__ float tile_weight(float s, float m, float c) {
-    return round_to_bf16(ex2(__fmul_rn(__fsub_rn(s, m), c)));
+// Softmax weight of one logit inside its tile, before rounding: exp2( s * c - m * c ), one fused
+// multiply-add with neg_mc = -(m * c).  A masked logit (-inf) gives exactly 0.
+__device__ __forceinline__ float tile_weight_raw(float s, float neg_mc, float c) {
+    return ex2(__fmaf_rn(s, c, neg_mc));
+}
+__device__ __forceinline__ float tile_weight(float s, float neg_mc, float c) {
+    return round_to_bf16(tile_weight_raw(s, neg_mc, c));
 }
 
 // One step of the fold: the coefficients, then the update of any accumulated quantity.

@@ -146,9 +146,15 @@ def test_c3_gemma_stack(hb, ctx):
         run.decode_step(cfg.prompt + step, cfg.prompt + step)
     ctx.check()
     rows = np.array([0, 1, 511, 512, 1023, 1024, 1500, 4095, 4096, 8191, 8192, 8195])
-    for layer in (0, 5):                                   # one local, the global one
-        want = oracle_rows(cfg, cfg.layers[layer], inputs.layers[layer], rows, cache=run.cache, layer=layer)
-        assert tl.within_tolerance(run.output(layer)[rows], want), layer
+    # The global layer (linear storage): every sampled row, attention checked over the cache's rows.
+    want = oracle_rows(cfg, cfg.layers[5], inputs.layers[5], rows, cache=run.cache, layer=5)
+    assert tl.within_tolerance(run.output(5)[rows], want)
+    # A local layer lives in a ring of 1536 rows at this context (8320 > 8192), so early keys are
+    # gone by now: its rows are checked against the oracle's own prologue.  The weightless v norm
+    # can land on a neighbouring bf16 value (one step is 2^-6 at |v| >= 2), hence the wider bound.
+    assert run.cache.layer(0).ring_size == 1536
+    want = oracle_rows(cfg, cfg.layers[0], inputs.layers[0], rows)
+    assert tl.within_tolerance(run.output(0)[rows], want, tol=2e-2)
     run.close()
 
 
