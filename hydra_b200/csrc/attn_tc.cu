@@ -624,8 +624,12 @@ template <int D>
 static hc_status launch_tc(hc_context* ctx, const TcArgs& args, const hc_layer_store& layer, cudaStream_t stream) {
     using LT = TcLayout<D>;
     const int smem = LT::kSmemBytes + int(sizeof(TcBarriers));
-    cudaError_t err = cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (err != cudaSuccess) return check_cuda(err, "attention_tc_kernel shared memory");
+    static bool configured[64] = {};                 // per device: the attribute is set once
+    if (!configured[ctx->device & 63]) {
+        cudaError_t err = cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (err != cudaSuccess) return check_cuda(err, "attention_tc_kernel shared memory");
+        configured[ctx->device & 63] = true;
+    }
     // Persistent: one CTA per SM at most, each walking items blockIdx.x, blockIdx.x + gridDim.x, ...
     const int grid = std::max(1, std::min(args.n_items, std::max(ctx->sm_count, 1)));
     attention_tc_kernel<D><<<grid, kTcThreads, smem, stream>>>(*static_cast<const CUtensorMap*>(layer.tmap_k),
