@@ -350,13 +350,28 @@ merge_tiles_kernel(const AttnShape shape, const BatchMeta meta, const float* __r
 
         // The sequential part.  Every thread carries L (same chain, same bits) and its columns.
         const float* o_base = part_o + (row * part_tiles + base) * d;
-        for (int t = 0; t < count; ++t) {
-            const float a = coef_a[t], bcoef = coef_b[t];
-            L = __fmaf_rn(L, a, part_l[t]);
+        // The partials are fetched eight tiles ahead of the dependent chain that consumes them.
+        constexpr int kAhead = 8;
+        for (int t0 = 0; t0 < count; t0 += kAhead) {
+            float part[kAhead][kCols];
             #pragma unroll
-            for (int cidx = 0; cidx < kCols; ++cidx) {
-                const int i = tid + cidx * kThreads;
-                if (i < d) A[cidx] = __fmaf_rn(A[cidx], a, __fmul_rn(o_base[size_t(t) * d + i], bcoef));
+            for (int u = 0; u < kAhead; ++u) {
+                #pragma unroll
+                for (int cidx = 0; cidx < kCols; ++cidx) {
+                    const int i = tid + cidx * kThreads;
+                    part[u][cidx] = (t0 + u < count && i < d) ? __ldg(o_base + size_t(t0 + u) * d + i) : 0.0f;
+                }
+            }
+            #pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                if (t0 + u < count) {
+                    const float a = coef_a[t0 + u], bcoef = coef_b[t0 + u];
+                    L = __fmaf_rn(L, a, part_l[t0 + u]);
+                    #pragma unroll
+                    for (int cidx = 0; cidx < kCols; ++cidx) {
+                        A[cidx] = __fmaf_rn(A[cidx], a, __fmul_rn(part[u][cidx], bcoef));
+                    }
+                }
             }
         }
         M = chunk_max;

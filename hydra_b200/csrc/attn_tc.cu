@@ -160,6 +160,19 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return packed;
 }
 
+// Optional timeline for bring-up builds (-DHC_TC_TRACE): nanosecond stamps of a few events per CTA.
+#ifdef HC_TC_TRACE
+__device__ unsigned long long hc_tc_trace[256 * 16];
+__device__ __forceinline__ void tc_trace(int slot) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+    if (blockIdx.x < 256 && hc_tc_trace[blockIdx.x * 16 + slot] == 0) hc_tc_trace[blockIdx.x * 16 + slot] = now;
+}
+#define TC_TRACE(slot) tc_trace(slot)
+#else
+#define TC_TRACE(slot)
+#endif
+
 template <int D>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
@@ -179,6 +192,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     volatile int* abort_flag = &bars->abort_flag;
 
     if (threadIdx.x == 0) {
+        TC_TRACE(0);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars->q_full[i], 128);
             mbar_init(&bars->q_empty[i], 1);
@@ -197,10 +211,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         fence_barrier_init();
     }
     if (warp == 1) tmem_alloc(&bars->tmem_base, LT::kTmemCols);
+    if (warp == 0 && lane == 0) {
+        prefetch_tensormap(&tmap_k);
+        prefetch_tensormap(&tmap_v);
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
+    if (threadIdx.x == 0) TC_TRACE(1);
 
     if (warp == 0) {
         // ===== producer: one stream of tiles across all of this CTA's items =====
@@ -232,6 +251,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         tma_load_3d(v_smem + slot * LT::kTileBytes + b * (kTileKeys * 128), &tmap_v,
                                     &bars->v_full[slot], b * 64, row0, plane);
                     }
+                    TC_TRACE(2);
                 }
             }
         }
@@ -245,7 +265,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 const int slot = int(t % LT::kStages);
                 const int qb = int(it & 1);
                 if (first && !mbar_wait(&bars->q_full[qb], (it >> 1) & 1, abort_flag, args.status, 4)) return false;
+                TC_TRACE(3);
                 if (!mbar_wait(&bars->k_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 3)) return false;
+                TC_TRACE(4);
                 tc_fence_after();
                 const uint32_t q_addr = smem_u32(q_smem + qb * LT::kQBytes);
                 const uint32_t k_addr = smem_u32(k_smem + slot * LT::kTileBytes);
@@ -330,6 +352,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
                 const int sb = int(t & 1);
                 if (!mbar_wait(&bars->s_full[sb], (t >> 1) & 1, abort_flag, args.status, 8)) { ok = false; break; }
+                if (threadIdx.x == 64) TC_TRACE(5);
                 tc_fence_after();
                 if (!warp_has_rows) {
                     // No query row lives in this quadrant: its P rows stay whatever they were and the
@@ -348,26 +371,32 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 HC_TMEM_LD32(s_tmem + 64, s[2]);
                 HC_TMEM_LD32(s_tmem + 96, s[3]);
                 tc_wait_ld();
-                float m = neg_inf;
-                if (c_lo <= 0 && c_hi >= kTileKeys - 1) {
-                    #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        #pragma unroll
-                        for (int i = 0; i < 32; ++i) m = fmaxf(m, __uint_as_float(s[q4][i]));
-                    }
-                } else {
+                if (!(c_lo <= 0 && c_hi >= kTileKeys - 1)) {
                     #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
                         #pragma unroll
                         for (int i = 0; i < 32; ++i) {
                             const int col = q4 * 32 + i;
-                            const float value = (col >= c_lo && col <= c_hi) ? __uint_as_float(s[q4][i]) : neg_inf;
-                            s[q4][i] = __float_as_uint(value);
-                            m = fmaxf(m, value);
+                            if (col < c_lo || col > c_hi) s[q4][i] = __float_as_uint(neg_inf);
                         }
                     }
                 }
+                // Row maximum: eight independent chains (the maximum is exact under any association).
+                float mx[8];
+                #pragma unroll
+                for (int u = 0; u < 8; ++u) mx[u] = __uint_as_float(s[0][u]);
+                #pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (q4 > 0 || i >= 8) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(s[q4][i]));
+                    }
+                }
+                const float m = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                      fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
                 const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
+                // The row sum has a fixed shape: each group of 32 columns is reduced by the butterfly
+                // tree (i with i + 16, then + 8, + 4, + 2, + 1), and the four groups are added in order.
                 float sum = 0.0f;
                 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
@@ -376,18 +405,33 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     for (int i = 0; i < 16; ++i) {
                         const float e0 = tile_weight_raw(__uint_as_float(s[q4][2 * i]), neg_mc, args.c);
                         const float e1 = tile_weight_raw(__uint_as_float(s[q4][2 * i + 1]), neg_mc, args.c);
-                        const uint32_t pk = pack_bf16x2(e0, e1);
-                        sum = __fadd_rn(sum, __uint_as_float(pk << 16));
-                        sum = __fadd_rn(sum, __uint_as_float(pk & 0xffff0000u));
-                        packed[i] = pk;
+                        packed[i] = pack_bf16x2(e0, e1);
                     }
                     HC_TMEM_ST16(s_tmem + q4 * 16, packed);
+                    // column c of the group is the low (even c) or high (odd c) half of packed[c / 2]
+                    float a[16];
+                    #pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t lo_word = packed[i >> 1], hi_word = packed[(i + 16) >> 1];
+                        const float x = __uint_as_float((i & 1) ? (lo_word & 0xffff0000u) : (lo_word << 16));
+                        const float y = __uint_as_float((i & 1) ? (hi_word & 0xffff0000u) : (hi_word << 16));
+                        a[i] = __fadd_rn(x, y);
+                    }
+                    #pragma unroll
+                    for (int i = 0; i < 8; ++i) a[i] = __fadd_rn(a[i], a[i + 8]);
+                    #pragma unroll
+                    for (int i = 0; i < 4; ++i) a[i] = __fadd_rn(a[i], a[i + 4]);
+                    a[0] = __fadd_rn(a[0], a[2]);
+                    a[1] = __fadd_rn(a[1], a[3]);
+                    const float group = __fadd_rn(a[0], a[1]);
+                    sum = q4 == 0 ? group : __fadd_rn(sum, group);
                 }
                 bars->mm[t & 3][row] = __fmul_rn(m, args.c);
                 bars->l[t & 3][row] = sum;
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[sb]);
+                if (threadIdx.x == 64) TC_TRACE(6);
             }
         }
     } else {
@@ -448,6 +492,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
                 const int ob = int(t % LT::kOBufs);
                 if (!mbar_wait(&bars->o_full[ob], (t / LT::kOBufs) & 1, abort_flag, args.status, 9)) { ok = false; break; }
+                if (threadIdx.x == 192) TC_TRACE(7);
                 tc_fence_after();
                 if (!warp_has_rows) {
                     tc_fence_before();
@@ -548,8 +593,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     }
                 }
             }
+            if (threadIdx.x == 192) TC_TRACE(8);
             item = nxt;
             ++it;
+        }
+        if (threadIdx.x == 192) {
+#ifdef HC_TC_TRACE
+            hc_tc_trace[(blockIdx.x & 255) * 16 + 9] = 0;
+#endif
+            TC_TRACE(9);
         }
     }
 
@@ -560,6 +612,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     }
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) TC_TRACE(10);
     if (warp == 1) tmem_dealloc(tmem, LT::kTmemCols);
 }
 
@@ -717,5 +770,17 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
     if (st != HC_OK) return st;
     return launch_merge(ctx, shape, meta, n_seq, ws, max_tiles, world, cache.map.rank, ep, stream);
 }
+
+#ifdef HC_TC_TRACE
+extern "C" __attribute__((visibility("default"))) int hc_debug_read_trace(unsigned long long* out, int clear) {
+    cudaDeviceSynchronize();
+    if (cudaMemcpyFromSymbol(out, hc_tc_trace, sizeof(hc_tc_trace)) != cudaSuccess) return -1;
+    if (clear) {
+        static unsigned long long zeros[256 * 16];
+        cudaMemcpyToSymbol(hc_tc_trace, zeros, sizeof(zeros));
+    }
+    return 0;
+}
+#endif
 
 }  // namespace hc

@@ -11,12 +11,14 @@
 //
 // One warp handles one head vector.  HBM-bound and tiny: a chunk of 512 tokens moves a few MB.
 
+#include <algorithm>
+
 #include "internal.hpp"
 
 namespace hc {
 namespace {
 
-constexpr int kPrepWarps = 4;
+constexpr int kPrepWarps = 8;
 constexpr int kMaxHeadDim = 512;
 
 __global__ void __launch_bounds__(kPrepWarps * 32)
@@ -29,9 +31,13 @@ prepare_heads_kernel(const PrepArgs args) {
 
     int total_heads = 0;
     for (int j = 0; j < args.n_jobs; ++j) total_heads += args.job[j].heads;
-    const int slot = blockIdx.x * kPrepWarps + warp;
-    const int token = blockIdx.y;
-    if (slot >= total_heads || token >= args.tokens) return;
+    // Warps stride over the (token, head) vectors of the call.
+    const long long vectors = (long long)args.tokens * total_heads;
+    const long long stride = (long long)gridDim.x * kPrepWarps;
+    for (long long vec = (long long)blockIdx.x * kPrepWarps + warp; vec < vectors; vec += stride) {
+    const int token = int(vec / total_heads);
+    const int slot = int(vec - (long long)token * total_heads);
+    __syncwarp();                                  // the staging row is reused
 
     int job_index = 0, head = slot;
     while (head >= args.job[job_index].heads) {
@@ -43,7 +49,7 @@ prepare_heads_kernel(const PrepArgs args) {
     const int position = args.batched ? args.meta.pos[token] : args.first_position + token;
     const int seq = args.batched ? args.meta.seq[token] : args.seq;
     if (job.kind == 1 || job.kind == 2) {
-        if (!row_is_local(args.cache.map, position)) return;   // another rank owns this key tile
+        if (!row_is_local(args.cache.map, position)) continue;   // another rank owns this key tile
     }
 
     float* x = stage[warp];
@@ -98,6 +104,7 @@ prepare_heads_kernel(const PrepArgs args) {
             dst16[half + i] = float_to_bf16_bits(x2);
         }
     }
+    }
 }
 
 __global__ void split_query_gate_kernel(const void* combined, void* query, void* gate, size_t count,
@@ -124,8 +131,9 @@ hc_status launch_prepare(hc_context* ctx, const PrepArgs& args, cudaStream_t str
     int total_heads = 0;
     for (int j = 0; j < args.n_jobs; ++j) total_heads += args.job[j].heads;
     if (total_heads == 0 || args.tokens == 0) return HC_OK;
-    if (args.tokens > 65535) return fail(HC_INVALID_ARGUMENT, "prologue: more than 65535 tokens in one launch");
-    dim3 grid((total_heads + kPrepWarps - 1) / kPrepWarps, args.tokens);
+    const long long vectors = (long long)args.tokens * total_heads;
+    const long long wanted = (vectors + kPrepWarps - 1) / kPrepWarps;
+    const int grid = int(std::min<long long>(wanted, (long long)std::max(ctx->sm_count, 1) * 8));
     prepare_heads_kernel<<<grid, kPrepWarps * 32, 0, stream>>>(args);
     ctx->launches += 1;
     return check_cuda(cudaGetLastError(), "prepare_heads_kernel launch");
