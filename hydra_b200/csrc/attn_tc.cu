@@ -162,15 +162,22 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 // Optional timeline for bring-up builds (-DHC_TC_TRACE): nanosecond stamps of a few events per CTA.
 #ifdef HC_TC_TRACE
-__device__ unsigned long long hc_tc_trace[256 * 16];
+__device__ unsigned long long hc_tc_trace[256 * 16 * 4];
 __device__ __forceinline__ void tc_trace(int slot) {
     unsigned long long now;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
     if (blockIdx.x < 256 && hc_tc_trace[blockIdx.x * 16 + slot] == 0) hc_tc_trace[blockIdx.x * 16 + slot] = now;
 }
 #define TC_TRACE(slot) tc_trace(slot)
+// Cycle accounting of one thread: TC_LAP(k) adds the cycles since the previous lap to bucket k.
+#define TC_LAP_DECL long long lap_last = clock64(); long long lap_acc[6] = {0, 0, 0, 0, 0, 0};
+#define TC_LAP(k) { const long long lap_now = clock64(); lap_acc[k] += lap_now - lap_last; lap_last = lap_now; }
+#define TC_LAP_STORE(base) { for (int lap_i = 0; lap_i < 6; ++lap_i) hc_tc_trace[(blockIdx.x & 255) * 16 + 16 * 256 * (base) + lap_i] = (unsigned long long)lap_acc[lap_i]; }
 #else
 #define TC_TRACE(slot)
+#define TC_LAP_DECL
+#define TC_LAP(k)
+#define TC_LAP_STORE(base)
 #endif
 
 template <int D>
@@ -343,6 +350,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         const float neg_inf = __int_as_float(0xff800000);
         uint32_t t = 0;
         bool ok = true;
+        TC_LAP_DECL
         for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item)) {
             const TcItem w = decode_item(args, item);
             const bool valid = t_local < w.valid_tokens;
@@ -351,7 +359,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const int lo = args.window > 0 ? max(0, pos - args.window + 1) : 0;
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
                 const int sb = int(t & 1);
+                TC_LAP(5)
                 if (!mbar_wait(&bars->s_full[sb], (t >> 1) & 1, abort_flag, args.status, 8)) { ok = false; break; }
+                TC_LAP(0)
                 if (threadIdx.x == 64) TC_TRACE(5);
                 tc_fence_after();
                 if (!warp_has_rows) {
@@ -371,6 +381,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 HC_TMEM_LD32(s_tmem + 64, s[2]);
                 HC_TMEM_LD32(s_tmem + 96, s[3]);
                 tc_wait_ld();
+                TC_LAP(1)
                 if (!(c_lo <= 0 && c_hi >= kTileKeys - 1)) {
                     #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
@@ -395,6 +406,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 const float m = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
                                       fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
                 const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
+                TC_LAP(2)
                 // The row sum has a fixed shape: each group of 32 columns is reduced by the butterfly
                 // tree (i with i + 16, then + 8, + 4, + 2, + 1), and the four groups are added in order.
                 float sum = 0.0f;
@@ -428,12 +440,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 }
                 bars->mm[t & 3][row] = __fmul_rn(m, args.c);
                 bars->l[t & 3][row] = sum;
+                TC_LAP(3)
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[sb]);
+                TC_LAP(4)
                 if (threadIdx.x == 64) TC_TRACE(6);
             }
         }
+        if (threadIdx.x == 64) { TC_LAP_STORE(1) }
     } else {
         // ===== fold + epilogue: thread = row; also stages the Q tiles =====
         const int quad = warp & 3;
@@ -776,7 +791,7 @@ extern "C" __attribute__((visibility("default"))) int hc_debug_read_trace(unsign
     cudaDeviceSynchronize();
     if (cudaMemcpyFromSymbol(out, hc_tc_trace, sizeof(hc_tc_trace)) != cudaSuccess) return -1;
     if (clear) {
-        static unsigned long long zeros[256 * 16];
+        static unsigned long long zeros[256 * 16 * 4];
         cudaMemcpyToSymbol(hc_tc_trace, zeros, sizeof(zeros));
     }
     return 0;
