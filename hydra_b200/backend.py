@@ -326,6 +326,23 @@ class AttentionBackend:
                                              _ints(positions), len(positions), _ptr(query),
                                              _ptr(output), ctypes.byref(s), _stream(stream)))
 
+    def attention_static(self, cache: KVCache, layer: int, query, output, positions, params: AttnParams,
+                         seq_ids=None, stream=None) -> None:
+        """`attention` for callers that may not allocate device memory: the split partials go to a
+        fixed 8 MiB array inside the library.  `query` must be bf16, already normalised and rotated."""
+        if isinstance(positions, int):
+            positions = [positions]
+        if seq_ids is None:
+            seq_ids = list(range(len(positions))) if len(positions) > 1 else [0]
+        s = params.struct()
+        _check(self._lib.hc_attention_decode_static(self.ctx.handle, cache.handle, layer, _ints(seq_ids),
+                                                    _ints(positions), len(positions), _ptr(query),
+                                                    _ptr(output), ctypes.byref(s), _stream(stream)))
+
+    @property
+    def static_scratch_limit(self) -> int:
+        return int(self._lib.hc_attention_decode_static_limit())
+
     # Sequence-sharded forms: partial per rank, then the combine every rank runs.
     def partial_bytes(self, params: AttnParams, rows: int) -> int:
         s = params.struct()

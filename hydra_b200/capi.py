@@ -83,6 +83,9 @@ _PROTOTYPES = {
                                      POINTER(AttnParamsStruct), _P]),
     "hc_attention_decode": (c_int, [_P, _P, c_int, POINTER(c_int), POINTER(c_int), c_int, _P, _P,
                                     POINTER(AttnParamsStruct), _P]),
+    "hc_attention_decode_static_limit": (c_size_t, []),
+    "hc_attention_decode_static": (c_int, [_P, _P, c_int, POINTER(c_int), POINTER(c_int), c_int, _P, _P,
+                                           POINTER(AttnParamsStruct), _P]),
     "hc_attention_partial_bytes": (c_size_t, [POINTER(AttnParamsStruct), c_int]),
     "hc_attention_prefill_partial": (c_int, [_P, _P, c_int, c_int, _P, _P, c_int, c_int,
                                              POINTER(AttnParamsStruct), _P]),

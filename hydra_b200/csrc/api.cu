@@ -301,6 +301,44 @@ hc_status decode_impl(hc_context* ctx, hc_kv_cache* cache, int layer, const int*
 }
 
 }  // namespace
+
+// Argument checking and kernel arguments for hc_attention_decode_static (attn_simt.cu).  Nothing
+// here allocates.
+hc_status static_decode_inputs(hc_context* ctx, hc_kv_cache* cache, int layer, const int* seq_ids,
+                               const int* positions, int n_seq, const void* q, void* out,
+                               const hc_attn_params* p, AttnShape* shape, CacheView* view, BatchMeta* meta,
+                               EpilogueArgs* ep) {
+    if (!ctx || !q || !out || !seq_ids || !positions) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    hc_status st = validate_params(cache, layer, p);
+    if (st != HC_OK) return st;
+    if (p->io_dtype != HC_BF16 || p->norm_q != 0 || p->rope != nullptr || p->gate_layout == HC_GATE_INTERLEAVED) {
+        return fail(HC_UNSUPPORTED, "hc_attention_decode_static takes a bf16 query that is already normalised and "
+                                    "rotated (io_dtype bf16, norm_q 0, rope NULL, gate none or separate)");
+    }
+    if (n_seq < 1 || n_seq > kMaxBatch) {
+        return fail(HC_INVALID_ARGUMENT, "hc_attention_decode_static takes 1 to " + std::to_string(kMaxBatch) + " sequences");
+    }
+    if (cache->shard.mode == HC_SHARD_SEQUENCE && cache->shard.world > 1) {
+        return fail(HC_UNSUPPORTED, "hc_attention_decode_static does not serve a sequence-sharded cache");
+    }
+    const hc_layer_store& L = cache->layers[size_t(layer)];
+    for (int b = 0; b < n_seq; ++b) {
+        if (seq_ids[b] < 0 || seq_ids[b] >= cache->max_seqs) return fail(HC_INVALID_ARGUMENT, "sequence index out of range");
+        st = check_positions(cache, L, positions[b], 1, p);
+        if (st != HC_OK) return st;
+        meta->seq[b] = seq_ids[b];
+        meta->pos[b] = positions[b];
+    }
+    *shape = shape_of(cache, p, false);
+    *view = view_of(cache, L);
+    ep->out = out;
+    ep->io_dtype = p->io_dtype;
+    ep->write_partial = 0;
+    ep->gate_layout = p->gate_layout;
+    ep->gate = p->gate;
+    return HC_OK;
+}
+
 }  // namespace hc
 
 using namespace hc;

@@ -552,4 +552,89 @@ hc_status launch_combine(hc_context* ctx, const float* gathered, int world, int 
     return check_cuda(cudaGetLastError(), "combine_ranks_kernel launch");
 }
 
+// ---- decode without any allocation ----------------------------------------------------------------
+//
+// Some hosts cannot allocate device memory at the moment they need attention: a runner that has
+// handed every byte of the device to its weight and KV pools, a plugin loaded into a process whose
+// allocator it must not touch, or a caller inside a region where cudaMalloc is forbidden.  For
+// them the split-decode partials live in this fixed array instead of a workspace that
+// hc_kv_cache_create would size.  Every GPU that loads the library holds these 8 MiB until the
+// process exits.
+constexpr size_t kStaticScratchFloats = size_t(2) << 20;               // 8 MiB
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+// `g_static_scratch` in host code is only a handle: the device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static float* static_scratch_address(int device, hc_status* status) {
+    static float* address[64] = {};
+    *status = HC_OK;
+    if (device < 0 || device >= 64) {
+        *status = fail(HC_INVALID_ARGUMENT, "device index out of range");
+        return nullptr;
+    }
+    if (!address[device]) {
+        int current = -1;
+        cudaError_t err = cudaGetDevice(&current);
+        if (err == cudaSuccess && current != device) err = cudaSetDevice(device);
+        void* ptr = nullptr;
+        if (err == cudaSuccess) err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (err != cudaSuccess || !ptr) {
+            *status = check_cuda(err == cudaSuccess ? cudaErrorInvalidSymbol : err, "address of the static decode scratch");
+            return nullptr;
+        }
+        address[device] = static_cast<float*>(ptr);
+    }
+    return address[device];
+}
+
+hc_status static_decode_inputs(hc_context* ctx, hc_kv_cache* cache, int layer, const int* seq_ids,
+                               const int* positions, int n_seq, const void* q, void* out,
+                               const hc_attn_params* p, AttnShape* shape, CacheView* view, BatchMeta* meta,
+                               EpilogueArgs* ep);
+
 }  // namespace hc
+
+extern "C" {
+
+size_t hc_attention_decode_static_limit(void) { return hc::kStaticScratchFloats * sizeof(float); }
+
+hc_status hc_attention_decode_static(hc_context* ctx, hc_kv_cache* cache, int layer, const int* seq_ids,
+                                     const int* positions, int n_seq, const void* q, void* out,
+                                     const hc_attn_params* params, void* stream) {
+    using namespace hc;
+    AttnShape shape{};
+    CacheView view{};
+    BatchMeta meta{};
+    EpilogueArgs ep{};
+    hc_status st = static_decode_inputs(ctx, cache, layer, seq_ids, positions, n_seq, q, out, params, &shape,
+                                        &view, &meta, &ep);
+    if (st != HC_OK) return st;
+    int max_tiles = 0;
+    for (int b = 0; b < n_seq; ++b) {
+        int lo, first_tile, last_tile;
+        tile_span(meta.pos[b], shape.window, lo, first_tile, last_tile);
+        max_tiles = std::max(max_tiles, last_tile - first_tile + 1);
+    }
+    // Partials: [rows][tiles][d] then [rows][tiles][2].
+    const size_t rows = size_t(n_seq) * shape.q_heads;
+    const size_t o_floats = rows * max_tiles * shape.head_dim;
+    const size_t need = o_floats + rows * max_tiles * 2;
+    if (need > kStaticScratchFloats) {
+        return fail(HC_KV_OVERFLOW, "hc_attention_decode_static: this call needs " + std::to_string(need * 4) +
+                                        " bytes of partials, the fixed scratch holds " +
+                                        std::to_string(kStaticScratchFloats * 4));
+    }
+    float* scratch = static_scratch_address(ctx->device, &st);
+    if (!scratch) return st;
+    // Every partial the merge reads is written by this call's split kernel first, so nothing in the
+    // array has to start at zero.
+    Workspace ws;
+    ws.part_o = scratch;
+    ws.part_ml = scratch + o_floats;
+    ws.part_o_floats = o_floats;
+    ws.part_ml_floats = rows * max_tiles * 2;
+    return simt_decode(ctx, shape, view, meta, n_seq, static_cast<const uint16_t*>(q), ws, ep,
+                       static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -265,6 +265,32 @@ HC_API hc_status hc_attention_decode(hc_context* ctx, hc_kv_cache* cache, int la
                                      const void* q, void* out, const hc_attn_params* params,
                                      void* stream);
 
+/* hc_attention_decode for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference, whose split partials come from a scratch pool grown on demand
+ * (Sources/HydraMetal/MetalContext.swift:108-116).
+ *
+ * Who needs it: a runner that has already given every free byte of the device to its weight and KV
+ * pools, a plugin that must not touch its host process's allocator, or code running where
+ * cudaMalloc is not allowed.  The split-decode partials of this call live in one fixed array
+ * inside the library (hc_attention_decode_static_limit() bytes, 8 MiB, held by every GPU that
+ * loads the library until the process exits) and the call performs no cudaMalloc, cudaFree or any
+ * other allocating routine.
+ *
+ *   - q must be bf16, already normalised and rotated: io_dtype HC_BF16, norm_q 0, rope NULL, gate
+ *     none or HC_GATE_SEPARATE.  1 to 64 sequences; not for sequence-sharded caches.
+ *   - A call whose partials (n_seq * q_heads * visible_tiles * (head_dim + 2) floats) exceed the
+ *     limit is refused with HC_KV_OVERFLOW and a message that states both sizes.
+ *   - The first call on a device looks the array's device address up (cudaGetSymbolAddress, with
+ *     that device current).  Make that first call outside any stream capture.
+ *   - All calls share the array and it keeps the last call's contents.  Nothing in it needs to be
+ *     zero beforehand: each call writes every partial before reading it.  Two calls that overlap on
+ *     the GPU (different streams, no dependency) race on it: serialise them. */
+HC_API size_t hc_attention_decode_static_limit(void);
+HC_API hc_status hc_attention_decode_static(hc_context* ctx, hc_kv_cache* cache, int layer,
+                                            const int* seq_ids, const int* positions, int n_seq,
+                                            const void* q, void* out, const hc_attn_params* params,
+                                            void* stream);
+
 /* Sequence-sharded attention, step 1 of 2 (no counterpart in the reference).  Like
  * hc_attention_prefill / hc_attention_decode over the key tiles this rank owns, but writes this
  * rank's unnormalised partial (running maximum, denominator, numerator) instead of the output:
