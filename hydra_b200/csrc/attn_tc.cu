@@ -575,9 +575,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 const size_t out_row = size_t(w.row0 + t_local);
                 if (args.ep.write_partial) {
                     float* dst = reinterpret_cast<float*>(args.ep.out) + (out_row * args.q_heads + head) * size_t(D + 2);
+                    // A partial row is D + 2 floats: its start is 8-byte aligned, not 16.
                     #pragma unroll
-                    for (int i = 0; i < D; i += 4) {
-                        *reinterpret_cast<float4*>(dst + i) = make_float4(A[i], A[i + 1], A[i + 2], A[i + 3]);
+                    for (int i = 0; i < D; i += 2) {
+                        *reinterpret_cast<float2*>(dst + i) = make_float2(A[i], A[i + 1]);
                     }
                     dst[D] = M;
                     dst[D + 1] = L;
