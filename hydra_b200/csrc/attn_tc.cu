@@ -74,18 +74,24 @@ struct TcLayout {
     static constexpr int kQBytes = kRows * D * 2;            // one Q tile; two are kept
     static constexpr int kSCol0 = 0, kSCol1 = 128;
     static constexpr int kOCol0 = 256;
+    // d = 64 leaves room beside each O buffer for 16 columns of row sums computed by the tensor core.
+    static constexpr bool kSumOnTensor = D == 64;
+    static constexpr int kOStride = kSumOnTensor ? D + 16 : D;
     static constexpr int kTmemCols = 512;
-    static constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + 2 * kStages * kTileBytes;
+    static constexpr int kOnesBytes = 2048;
+    static constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + 2 * kStages * kTileBytes + kOnesBytes;
 };
 
 struct TcBarriers {
     uint64_t q_full[2], q_empty[2];
     uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
     uint64_t s_full[2], p_full[2], o_full[2], o_free[2];
+    uint64_t x_bar[4];        // per lane quadrant: the two softmax warps that share a row exchange maxima
     uint32_t tmem_base;
     int abort_flag;
-    float mm[4][kRows];       // per-tile scaled maxima and sums, softmax -> fold (ring of 4 tiles)
-    float l[4][kRows];
+    float mm[4][kRows];       // per-tile scaled maxima, softmax -> fold (ring of 4 tiles)
+    float l[4][2][kRows];     // per-tile sums of each 64-column half (when not summed on the tensor core)
+    float xmax[2][2][kRows];  // per S buffer and half: that half's maximum
 };
 
 // One unit of work of a CTA.
@@ -190,10 +196,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     unsigned char* q_smem = base;                                  // two Q tiles
     unsigned char* k_smem = q_smem + 2 * LT::kQBytes;
     unsigned char* v_smem = k_smem + LT::kStages * LT::kTileBytes;
-    TcBarriers* bars = reinterpret_cast<TcBarriers*>(v_smem + LT::kStages * LT::kTileBytes);
+    unsigned char* ones_smem = v_smem + LT::kStages * LT::kTileBytes;   // 2 KiB of bf16 1.0
+    TcBarriers* bars = reinterpret_cast<TcBarriers*>(ones_smem + LT::kOnesBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int wg = warp >> 2;                                      // 0 control, 1-2 softmax halves, 3 fold
     const int G = 1 << args.log_group;
     const int world = max(args.map.world, 1);
     volatile int* abort_flag = &bars->abort_flag;
@@ -204,11 +212,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             mbar_init(&bars->q_full[i], 128);
             mbar_init(&bars->q_empty[i], 1);
             mbar_init(&bars->s_full[i], 1);
-            mbar_init(&bars->p_full[i], 128);
+            mbar_init(&bars->p_full[i], 256);
             mbar_init(&bars->o_full[i], 1);
             mbar_init(&bars->o_free[i], 128);
         }
         for (int i = 0; i < 4; ++i) {
+            mbar_init(&bars->x_bar[i], 64);
             mbar_init(&bars->k_full[i], 1);
             mbar_init(&bars->k_empty[i], 1);
             mbar_init(&bars->v_full[i], 1);
@@ -217,6 +226,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         bars->abort_flag = 0;
         fence_barrier_init();
     }
+    // The constant B operand of the row-sum MMA: every element is bf16 1.0, so any layout reads it.
+    for (int i = threadIdx.x; i < LT::kOnesBytes / 4; i += kTcThreads) {
+        reinterpret_cast<uint32_t*>(ones_smem)[i] = 0x3F803F80u;
+    }
+    fence_proxy_async();
     if (warp == 1) tmem_alloc(&bars->tmem_base, LT::kTmemCols);
     if (warp == 0 && lane == 0) {
         prefetch_tensormap(&tmap_k);
@@ -228,6 +242,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     const uint32_t tmem = bars->tmem_base;
     if (threadIdx.x == 0) TC_TRACE(1);
 
+    // Registers follow the work (setmaxnreg, first thing in each warpgroup's branch): the fold
+    // warpgroup holds a row of O per thread, the control warpgroup needs almost none.
+    if (wg == 0) {
+    reg_dealloc<48>();
     if (warp == 0) {
         // ===== producer: one stream of tiles across all of this CTA's items =====
         if (lane == 0) {
@@ -267,6 +285,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc(kTileKeys, false);
             constexpr uint32_t idesc_pv = instr_desc(D, true);
+            constexpr uint32_t idesc_sum = instr_desc(16, false);
+            const uint64_t ones_desc = smem_desc(smem_u32(ones_smem), 16);
             // S = Q K^T of stream tile t; `it` is the ordinal of its item, `last` marks its item's last tile.
             auto issue_qk = [&](uint32_t t, uint32_t it, bool first, bool last) -> bool {
                 const int slot = int(t % LT::kStages);
@@ -302,7 +322,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 ok = issue_qk(0, 0, true, w.n_tiles == 1);
             }
             while (ok) {
-                // Stream tile t is tile j of `w`.  Look ahead to t + 1.
                 int nxt = item;
                 TcItem wn = w;
                 for (int j = 0; ok && j < w.n_tiles; ++j, ++t) {
@@ -325,11 +344,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     tc_fence_after();
                     const uint32_t v_addr = smem_u32(v_smem + slot * LT::kTileBytes);
                     const uint32_t p_tmem = tmem + ((t & 1) ? LT::kSCol1 : LT::kSCol0);
-                    const uint32_t o_tmem = tmem + LT::kOCol0 + ob * D;
+                    const uint32_t o_tmem = tmem + LT::kOCol0 + ob * LT::kOStride;
                     #pragma unroll
                     for (int ks = 0; ks < kTileKeys / 16; ++ks) {
                         mma_ts(o_tmem, p_tmem + ks * 8, smem_desc(v_addr + ks * 2048, kTileKeys * 128), idesc_pv,
                                ks != 0 ? 1u : 0u);
+                    }
+                    if (LT::kSumOnTensor) {
+                        // Row sums of P on the tensor core: P x ones, 16 identical columns beside O.
+                        #pragma unroll
+                        for (int ks = 0; ks < kTileKeys / 16; ++ks) {
+                            mma_ts(o_tmem + D, p_tmem + ks * 8, ones_desc, idesc_sum, ks != 0 ? 1u : 0u);
+                        }
                     }
                     tc_commit(&bars->v_empty[slot]);
                     tc_commit(&bars->o_full[ob]);
@@ -341,14 +367,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             }
         }
     }
-    else if (warp < 6) {
-        // ===== softmax: thread = row =====
+    } else if (wg == 1 || wg == 2) {
+        // ===== softmax: two threads per row, one per 64-column half of the tile =====
+        reg_dealloc<112>();
+        const int half = wg - 1;                             // 0: columns 0-63, 1: columns 64-127
         const int quad = warp & 3;                           // the TMEM lane quadrant this warp may touch
         const int row = quad * 32 + lane;
         const int t_local = row >> args.log_group;
         const uint32_t lane_base = uint32_t(quad * 32) << 16;
         const float neg_inf = __int_as_float(0xff800000);
-        uint32_t t = 0;
+        uint32_t t = 0, xuse = 0;
         bool ok = true;
         TC_LAP_DECL
         for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item)) {
@@ -362,7 +390,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 TC_LAP(5)
                 if (!mbar_wait(&bars->s_full[sb], (t >> 1) & 1, abort_flag, args.status, 8)) { ok = false; break; }
                 TC_LAP(0)
-                if (threadIdx.x == 64) TC_TRACE(5);
+                if (threadIdx.x == 128) TC_TRACE(5);
                 tc_fence_after();
                 if (!warp_has_rows) {
                     // No query row lives in this quadrant: its P rows stay whatever they were and the
@@ -372,85 +400,92 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     continue;
                 }
                 const uint32_t s_tmem = tmem + lane_base + (sb ? LT::kSCol1 : LT::kSCol0);
-                const int key0 = (w.tile_first + j * world) * kTileKeys;
-                const int c_lo = lo - key0;                  // visible columns: [c_lo, c_hi]
+                const int key0 = (w.tile_first + j * world) * kTileKeys + half * 64;
+                const int c_lo = lo - key0;                  // visible columns of this half: [c_lo, c_hi]
                 const int c_hi = pos - key0;
-                uint32_t s[4][32];
-                HC_TMEM_LD32(s_tmem + 0, s[0]);
-                HC_TMEM_LD32(s_tmem + 32, s[1]);
-                HC_TMEM_LD32(s_tmem + 64, s[2]);
-                HC_TMEM_LD32(s_tmem + 96, s[3]);
+                uint32_t s[2][32];
+                HC_TMEM_LD32(s_tmem + half * 64, s[0]);
+                HC_TMEM_LD32(s_tmem + half * 64 + 32, s[1]);
                 tc_wait_ld();
                 TC_LAP(1)
-                if (!(c_lo <= 0 && c_hi >= kTileKeys - 1)) {
+                if (!(c_lo <= 0 && c_hi >= 63)) {
                     #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
+                    for (int q2 = 0; q2 < 2; ++q2) {
                         #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            const int col = q4 * 32 + i;
-                            if (col < c_lo || col > c_hi) s[q4][i] = __float_as_uint(neg_inf);
+                            const int col = q2 * 32 + i;
+                            if (col < c_lo || col > c_hi) s[q2][i] = __float_as_uint(neg_inf);
                         }
                     }
                 }
-                // Row maximum: eight independent chains (the maximum is exact under any association).
-                float mx[8];
+                // Maximum of this half (exact under any association), then of the row through shared memory.
+                float mx[4];
                 #pragma unroll
-                for (int u = 0; u < 8; ++u) mx[u] = __uint_as_float(s[0][u]);
-                #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
+                for (int u = 0; u < 4; ++u) {
+                    float acc = __uint_as_float(s[0][u]);
                     #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (q4 > 0 || i >= 8) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(s[q4][i]));
+                    for (int k = 1; k < 15; k += 2) {
+                        const int i0 = u + 4 * k, i1 = u + 4 * (k + 1);
+                        acc = fmax3(acc, __uint_as_float(s[i0 >> 5][i0 & 31]), __uint_as_float(s[i1 >> 5][i1 & 31]));
                     }
+                    mx[u] = fmaxf(acc, __uint_as_float(s[1][28 + u]));
                 }
-                const float m = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
-                                      fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+                const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                bars->xmax[sb][half][row] = m_half;
+                mbar_arrive(&bars->x_bar[quad]);             // the two warps that share this quadrant
+                if (!mbar_wait(&bars->x_bar[quad], xuse & 1, abort_flag, args.status, 11)) { ok = false; break; }
+                ++xuse;
+                const float m = fmaxf(m_half, bars->xmax[sb][half ^ 1][row]);
                 const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
                 TC_LAP(2)
-                // The row sum has a fixed shape: each group of 32 columns is reduced by the butterfly
-                // tree (i with i + 16, then + 8, + 4, + 2, + 1), and the four groups are added in order.
-                float sum = 0.0f;
+                uint32_t packed[32];
                 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    uint32_t packed[16];
+                for (int q2 = 0; q2 < 2; ++q2) {
                     #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float e0 = tile_weight_raw(__uint_as_float(s[q4][2 * i]), neg_mc, args.c);
-                        const float e1 = tile_weight_raw(__uint_as_float(s[q4][2 * i + 1]), neg_mc, args.c);
-                        packed[i] = pack_bf16x2(e0, e1);
+                        const float e0 = tile_weight_raw(__uint_as_float(s[q2][2 * i]), neg_mc, args.c);
+                        const float e1 = tile_weight_raw(__uint_as_float(s[q2][2 * i + 1]), neg_mc, args.c);
+                        packed[q2 * 16 + i] = pack_bf16x2(e0, e1);
                     }
-                    HC_TMEM_ST16(s_tmem + q4 * 16, packed);
-                    // column c of the group is the low (even c) or high (odd c) half of packed[c / 2]
-                    float a[16];
-                    #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const uint32_t lo_word = packed[i >> 1], hi_word = packed[(i + 16) >> 1];
-                        const float x = __uint_as_float((i & 1) ? (lo_word & 0xffff0000u) : (lo_word << 16));
-                        const float y = __uint_as_float((i & 1) ? (hi_word & 0xffff0000u) : (hi_word << 16));
-                        a[i] = __fadd_rn(x, y);
-                    }
-                    #pragma unroll
-                    for (int i = 0; i < 8; ++i) a[i] = __fadd_rn(a[i], a[i + 8]);
-                    #pragma unroll
-                    for (int i = 0; i < 4; ++i) a[i] = __fadd_rn(a[i], a[i + 4]);
-                    a[0] = __fadd_rn(a[0], a[2]);
-                    a[1] = __fadd_rn(a[1], a[3]);
-                    const float group = __fadd_rn(a[0], a[1]);
-                    sum = q4 == 0 ? group : __fadd_rn(sum, group);
+                    HC_TMEM_ST16(s_tmem + half * 32 + q2 * 16, (&packed[q2 * 16]));
                 }
-                bars->mm[t & 3][row] = __fmul_rn(m, args.c);
-                bars->l[t & 3][row] = sum;
+                if (!LT::kSumOnTensor) {
+                    // Sum of this half's 64 weights: two groups of 32, each by the butterfly tree
+                    // (i with i + 16, then + 8, + 4, + 2, + 1), then the two groups added.
+                    float part[2];
+                    #pragma unroll
+                    for (int q2 = 0; q2 < 2; ++q2) {
+                        float a[16];
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const uint32_t lo_word = packed[q2 * 16 + (i >> 1)], hi_word = packed[q2 * 16 + ((i + 16) >> 1)];
+                            const float x = __uint_as_float((i & 1) ? (lo_word & 0xffff0000u) : (lo_word << 16));
+                            const float y = __uint_as_float((i & 1) ? (hi_word & 0xffff0000u) : (hi_word << 16));
+                            a[i] = __fadd_rn(x, y);
+                        }
+                        #pragma unroll
+                        for (int i = 0; i < 8; ++i) a[i] = __fadd_rn(a[i], a[i + 8]);
+                        #pragma unroll
+                        for (int i = 0; i < 4; ++i) a[i] = __fadd_rn(a[i], a[i + 4]);
+                        a[0] = __fadd_rn(a[0], a[2]);
+                        a[1] = __fadd_rn(a[1], a[3]);
+                        part[q2] = __fadd_rn(a[0], a[1]);
+                    }
+                    bars->l[t & 3][half][row] = __fadd_rn(part[0], part[1]);
+                }
+                if (half == 0) bars->mm[t & 3][row] = __fmul_rn(m, args.c);
                 TC_LAP(3)
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[sb]);
                 TC_LAP(4)
-                if (threadIdx.x == 64) TC_TRACE(6);
+                if (threadIdx.x == 128) TC_TRACE(6);
             }
         }
-        if (threadIdx.x == 64) { TC_LAP_STORE(1) }
+        if (threadIdx.x == 128) { TC_LAP_STORE(1) }
     } else {
         // ===== fold + epilogue: thread = row; also stages the Q tiles =====
+        reg_alloc<232>();
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int t_local = row >> args.log_group;
@@ -472,6 +507,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             }
             fence_proxy_async();
             mbar_arrive(&bars->q_full[qb]);
+        };
+        // The tile's row sum: from the tensor core (column D of the O buffer) or the two halves' sums.
+        auto tile_sum = [&](uint32_t o_tmem, uint32_t t) -> float {
+            if (LT::kSumOnTensor) {
+                const uint32_t bits = tmem_ld1(o_tmem + D);
+                tc_wait_ld();
+                return __uint_as_float(bits);
+            }
+            return __fadd_rn(bars->l[t & 3][0][row], bars->l[t & 3][1][row]);
         };
         uint32_t t = 0, it = 0;
         bool ok = true;
@@ -507,29 +551,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
                 const int ob = int(t % LT::kOBufs);
                 if (!mbar_wait(&bars->o_full[ob], (t / LT::kOBufs) & 1, abort_flag, args.status, 9)) { ok = false; break; }
-                if (threadIdx.x == 192) TC_TRACE(7);
+                if (threadIdx.x == 384) TC_TRACE(7);
                 tc_fence_after();
                 if (!warp_has_rows) {
                     tc_fence_before();
                     mbar_arrive(&bars->o_free[ob]);
                     continue;
                 }
-                const uint32_t o_tmem = tmem + lane_base + LT::kOCol0 + ob * D;
+                const uint32_t o_tmem = tmem + lane_base + LT::kOCol0 + ob * LT::kOStride;
+                const float l_tile = tile_sum(o_tmem, t);
                 if (args.decode) {
                     // Split decode: the tile's partial goes to the workspace; merge_tiles_kernel folds.
                     const size_t prow = (size_t(w.row0) * args.q_heads + head) * args.part_tiles + (w.ordinal0 + j);
                     #pragma unroll
-                    for (int half = 0; half < D / 64; ++half) {
+                    for (int hb = 0; hb < D / 64; ++hb) {
                         uint32_t o[2][32];
-                        HC_TMEM_LD32(o_tmem + half * 64, o[0]);
-                        HC_TMEM_LD32(o_tmem + half * 64 + 32, o[1]);
+                        HC_TMEM_LD32(o_tmem + hb * 64, o[0]);
+                        HC_TMEM_LD32(o_tmem + hb * 64 + 32, o[1]);
                         tc_wait_ld();
-                        if (half == D / 64 - 1) {
+                        if (hb == D / 64 - 1) {
                             tc_fence_before();
                             mbar_arrive(&bars->o_free[ob]);
                         }
                         if (valid) {
-                            float* dst = args.part_o + prow * D + half * 64;
+                            float* dst = args.part_o + prow * D + hb * 64;
                             #pragma unroll
                             for (int u = 0; u < 2; ++u) {
                                 #pragma unroll
@@ -542,21 +587,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     }
                     if (valid) {
                         args.part_ml[prow * 2] = bars->mm[t & 3][row];
-                        args.part_ml[prow * 2 + 1] = bars->l[t & 3][row];
+                        args.part_ml[prow * 2 + 1] = l_tile;
                     }
                     continue;
                 }
                 float Mn, a, b;
                 fold_coefficients(M, bars->mm[t & 3][row], Mn, a, b);
-                L = __fmaf_rn(L, a, __fmul_rn(bars->l[t & 3][row], b));
+                L = __fmaf_rn(L, a, __fmul_rn(l_tile, b));
                 M = Mn;
                 #pragma unroll
-                for (int half = 0; half < D / 64; ++half) {
+                for (int hb = 0; hb < D / 64; ++hb) {
                     uint32_t o[2][32];
-                    HC_TMEM_LD32(o_tmem + half * 64, o[0]);
-                    HC_TMEM_LD32(o_tmem + half * 64 + 32, o[1]);
+                    HC_TMEM_LD32(o_tmem + hb * 64, o[0]);
+                    HC_TMEM_LD32(o_tmem + hb * 64 + 32, o[1]);
                     tc_wait_ld();
-                    if (half == D / 64 - 1) {
+                    if (hb == D / 64 - 1) {
                         tc_fence_before();
                         mbar_arrive(&bars->o_free[ob]);
                     }
@@ -564,7 +609,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     for (int u = 0; u < 2; ++u) {
                         #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            const int col = half * 64 + u * 32 + i;
+                            const int col = hb * 64 + u * 32 + i;
                             A[col] = fold_value(A[col], a, __uint_as_float(o[u][i]), b);
                         }
                     }
@@ -609,11 +654,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     }
                 }
             }
-            if (threadIdx.x == 192) TC_TRACE(8);
+            if (threadIdx.x == 384) TC_TRACE(8);
             item = nxt;
             ++it;
         }
-        if (threadIdx.x == 192) {
+        if (threadIdx.x == 384) {
 #ifdef HC_TC_TRACE
             hc_tc_trace[(blockIdx.x & 255) * 16 + 9] = 0;
 #endif
