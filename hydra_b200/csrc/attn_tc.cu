@@ -71,10 +71,11 @@ struct TcLayout {
     static constexpr int kTileBytes = kTileKeys * D * 2;     // one K or V tile
     static constexpr int kStages = D == 64 ? 4 : 2;
     static constexpr int kQBytes = kRows * D * 2;            // one Q tile; two are kept
-    // Tensor memory: three S buffers of 128 columns (P overwrites the first 64 of its S), then one
-    // O buffer; d = 64 leaves room beside it for 16 columns of row sums computed by the tensor core.
-    static constexpr int kOCol0 = 3 * kTileKeys;
+    // Tensor memory: two S buffers of 128 columns (P overwrites the first 64 of its S), then two
+    // O buffers; d = 64 leaves room beside each for 16 columns of row sums computed by the tensor core.
+    static constexpr int kOCol0 = 2 * kTileKeys;
     static constexpr bool kSumOnTensor = D == 64;
+    static constexpr int kOStride = kSumOnTensor ? D + 16 : D;
     static constexpr int kTmemCols = 512;
     static constexpr int kOnesBytes = 2048;
     static constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + 2 * kStages * kTileBytes + kOnesBytes;
@@ -83,7 +84,7 @@ struct TcLayout {
 struct TcBarriers {
     uint64_t q_full[2], q_empty[2];
     uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
-    uint64_t s_full[3], p_full[3], o_full, o_free;
+    uint64_t s_full[2], p_full[2], o_full[2], o_free[2];
     uint32_t tmem_base;
     int abort_flag;
     float mm[4][kRows];       // per-tile scaled maxima, softmax -> fold (ring of 4 tiles)
@@ -233,12 +234,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             mbar_init(&bars->q_full[i], 128);
             mbar_init(&bars->q_empty[i], 1);
         }
-        for (int i = 0; i < 3; ++i) {
+        for (int i = 0; i < 2; ++i) {
             mbar_init(&bars->s_full[i], 1);
             mbar_init(&bars->p_full[i], 128);
+            mbar_init(&bars->o_full[i], 1);
+            mbar_init(&bars->o_free[i], 128);
         }
-        mbar_init(&bars->o_full, 1);
-        mbar_init(&bars->o_free, 128);
         for (int i = 0; i < 4; ++i) {
             mbar_init(&bars->k_full[i], 1);
             mbar_init(&bars->k_empty[i], 1);
@@ -302,7 +303,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             auto issue_qk = [&](const TcCursor& c) -> bool {
                 const int slot = int(c.t % LT::kStages);
                 const int qb = int(c.it & 1);
-                const int sb = int(c.t % 3);
+                const int sb = int(c.t & 1);
                 if (c.j == 0 && !mbar_wait(&bars->q_full[qb], (c.it >> 1) & 1, abort_flag, args.status, 4)) return false;
                 TC_TRACE(3);
                 if (!mbar_wait(&bars->k_full[slot], (c.t / LT::kStages) & 1, abort_flag, args.status, 3)) return false;
@@ -328,21 +329,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             TcCursor ahead = cursor_begin(args);          // next tile whose S is to be issued
             bool ok = true;
             for (TcCursor c = cursor_begin(args); ok && cursor_valid(args, c); cursor_advance(args, c)) {
-                // S buffer (t + 2) % 3 was last read as P by tile t - 1, whose MMAs are already queued.
-                while (ok && cursor_valid(args, ahead) && ahead.t < c.t + 3) {
+                // S of tile t + 1 goes to the buffer tile t - 1 used; its P V is already queued.  The
+                // look-ahead never waits for a Q tile beyond the next item's: that one is staged only
+                // after the fold warpgroup has seen this item's outputs.
+                while (ok && cursor_valid(args, ahead) && ahead.t < c.t + 2 && ahead.it <= c.it + 1) {
                     ok = issue_qk(ahead);
                     cursor_advance(args, ahead);
                 }
                 if (!ok) break;
                 const int slot = int(c.t % LT::kStages);
-                const int sb = int(c.t % 3);
-                if (!mbar_wait(&bars->p_full[sb], (c.t / 3) & 1, abort_flag, args.status, 5)) break;
+                const int sb = int(c.t & 1);
+                if (!mbar_wait(&bars->p_full[sb], (c.t >> 1) & 1, abort_flag, args.status, 5)) break;
                 if (!mbar_wait(&bars->v_full[slot], (c.t / LT::kStages) & 1, abort_flag, args.status, 6)) break;
-                if (c.t >= 1 && !mbar_wait(&bars->o_free, (c.t - 1) & 1, abort_flag, args.status, 7)) break;
+                if (c.t >= 2 && !mbar_wait(&bars->o_free[sb], ((c.t >> 1) - 1) & 1, abort_flag, args.status, 7)) break;
                 tc_fence_after();
                 const uint32_t v_addr = smem_u32(v_smem + slot * LT::kTileBytes);
                 const uint32_t p_tmem = tmem + sb * kTileKeys;
-                const uint32_t o_tmem = tmem + LT::kOCol0;
+                const uint32_t o_tmem = tmem + LT::kOCol0 + sb * LT::kOStride;
                 #pragma unroll
                 for (int ks = 0; ks < kTileKeys / 16; ++ks) {
                     mma_ts(o_tmem, p_tmem + ks * 8, smem_desc(v_addr + ks * 2048, kTileKeys * 128), idesc_pv,
@@ -356,7 +359,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     }
                 }
                 tc_commit(&bars->v_empty[slot]);
-                tc_commit(&bars->o_full);
+                tc_commit(&bars->o_full[sb]);
             }
         }
     }
@@ -377,9 +380,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const bool warp_has_rows = quad * 32 < (c.w.valid_tokens << args.log_group);   // warp-uniform
             const int pos = valid ? c.w.first_pos + t_local : -1;
             const int lo = args.window > 0 ? max(0, pos - args.window + 1) : 0;
-            const int sb = int(c.t % 3);
+            const int sb = int(c.t & 1);
             TC_LAP(5)
-            if (!mbar_wait(&bars->s_full[sb], (c.t / 3) & 1, abort_flag, args.status, 8)) break;
+            if (!mbar_wait(&bars->s_full[sb], (c.t >> 1) & 1, abort_flag, args.status, 8)) break;
             TC_LAP(0)
             if (threadIdx.x == 128) TC_TRACE(5);
             tc_fence_after();
@@ -490,7 +493,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         const int t_local = row >> args.log_group;
         const int g = row & (G - 1);
         const uint32_t lane_base = uint32_t(quad * 32) << 16;
-        const uint32_t o_tmem = tmem + lane_base + LT::kOCol0;
         // This thread copies its own row of an item's Q tile into the swizzled K-major layout.
         auto stage_q = [&](const TcItem& w, int qb) {
             const bool valid = t_local < w.valid_tokens;
@@ -540,12 +542,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             #pragma unroll
             for (int i = 0; i < D; ++i) A[i] = 0.0f;
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
-                if (!mbar_wait(&bars->o_full, t & 1, abort_flag, args.status, 9)) { ok = false; break; }
+                const int ob = int(t & 1);
+                const uint32_t o_tmem = tmem + lane_base + LT::kOCol0 + ob * LT::kOStride;
+                if (!mbar_wait(&bars->o_full[ob], (t >> 1) & 1, abort_flag, args.status, 9)) { ok = false; break; }
                 if (threadIdx.x == 384) TC_TRACE(7);
                 tc_fence_after();
                 if (!warp_has_rows) {
                     tc_fence_before();
-                    mbar_arrive(&bars->o_free);
+                    mbar_arrive(&bars->o_free[ob]);
                     continue;
                 }
                 // The tile's row sum: column D of the O buffer (tensor core) or the softmax thread's sum.
@@ -569,7 +573,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         tc_wait_ld();
                         if (hb == D / 64 - 1) {
                             tc_fence_before();
-                            mbar_arrive(&bars->o_free);
+                            mbar_arrive(&bars->o_free[ob]);
                         }
                         if (valid) {
                             float* dst = args.part_o + prow * D + hb * 64;
@@ -601,7 +605,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     tc_wait_ld();
                     if (hb == D / 64 - 1) {
                         tc_fence_before();
-                        mbar_arrive(&bars->o_free);
+                        mbar_arrive(&bars->o_free[ob]);
                     }
                     #pragma unroll
                     for (int u = 0; u < 2; ++u) {
