@@ -70,10 +70,11 @@ struct TcLayout {
     static constexpr int kBlocks = D / 64;                   // 64-element (128-byte) column blocks
     static constexpr int kTileBytes = kTileKeys * D * 2;     // one K or V tile
     static constexpr int kStages = D == 64 ? 4 : 2;
+    static constexpr int kOBufs = 2;
     static constexpr int kQBytes = kRows * D * 2;            // one Q tile; two are kept
-    // Tensor memory: two S buffers of 128 columns (P overwrites the first 64 of its S), then two
-    // O buffers; d = 64 leaves room beside each for 16 columns of row sums computed by the tensor core.
-    static constexpr int kOCol0 = 2 * kTileKeys;
+    static constexpr int kSCol0 = 0, kSCol1 = 128;
+    static constexpr int kOCol0 = 256;
+    // d = 64 leaves room beside each O buffer for 16 columns of row sums computed by the tensor core.
     static constexpr bool kSumOnTensor = D == 64;
     static constexpr int kOStride = kSumOnTensor ? D + 16 : D;
     static constexpr int kTmemCols = 512;
@@ -85,10 +86,12 @@ struct TcBarriers {
     uint64_t q_full[2], q_empty[2];
     uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
     uint64_t s_full[2], p_full[2], o_full[2], o_free[2];
+    uint64_t x_bar[4];        // per lane quadrant: the two softmax warps that share a row exchange maxima
     uint32_t tmem_base;
     int abort_flag;
     float mm[4][kRows];       // per-tile scaled maxima, softmax -> fold (ring of 4 tiles)
-    float l[4][kRows];        // per-tile row sums (when they are not computed on the tensor core)
+    float l[4][2][kRows];     // per-tile sums of each 64-column half (when not summed on the tensor core)
+    float xmax[2][2][kRows];  // per S buffer and half: that half's maximum
 };
 
 // One unit of work of a CTA.
@@ -183,31 +186,6 @@ __device__ __forceinline__ void tc_trace(int slot) {
 #define TC_LAP_STORE(base)
 #endif
 
-// A position in the stream of key tiles a CTA processes: tile j of the item with ordinal `it`.
-struct TcCursor {
-    int item;          // index in the work list, or n_items at the end
-    TcItem w;
-    int j;             // tile within the item
-    uint32_t t;        // ordinal of the tile in the CTA's stream
-    uint32_t it;       // ordinal of the item
-};
-__device__ __forceinline__ TcCursor cursor_begin(const TcArgs& args) {
-    TcCursor c{};
-    c.item = first_item(args);
-    if (c.item < args.n_items) c.w = decode_item(args, c.item);
-    return c;
-}
-__device__ __forceinline__ bool cursor_valid(const TcArgs& args, const TcCursor& c) { return c.item < args.n_items; }
-__device__ __forceinline__ void cursor_advance(const TcArgs& args, TcCursor& c) {
-    ++c.t;
-    if (++c.j >= c.w.n_tiles) {
-        c.item = next_item(args, c.item);
-        if (c.item < args.n_items) c.w = decode_item(args, c.item);
-        c.j = 0;
-        ++c.it;
-    }
-}
-
 template <int D>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
@@ -223,7 +201,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int wg = warp >> 2;                                      // 0 control, 1-2 softmax (even / odd tiles), 3 fold
+    const int wg = warp >> 2;                                      // 0 control, 1-2 softmax halves, 3 fold
     const int G = 1 << args.log_group;
     const int world = max(args.map.world, 1);
     volatile int* abort_flag = &bars->abort_flag;
@@ -233,14 +211,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars->q_full[i], 128);
             mbar_init(&bars->q_empty[i], 1);
-        }
-        for (int i = 0; i < 2; ++i) {
             mbar_init(&bars->s_full[i], 1);
-            mbar_init(&bars->p_full[i], 128);
+            mbar_init(&bars->p_full[i], 256);
             mbar_init(&bars->o_full[i], 1);
             mbar_init(&bars->o_free[i], 128);
         }
         for (int i = 0; i < 4; ++i) {
+            mbar_init(&bars->x_bar[i], 64);
             mbar_init(&bars->k_full[i], 1);
             mbar_init(&bars->k_empty[i], 1);
             mbar_init(&bars->v_full[i], 1);
@@ -272,46 +249,56 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     if (warp == 0) {
         // ===== producer: one stream of tiles across all of this CTA's items =====
         if (lane == 0) {
-            for (TcCursor c = cursor_begin(args); cursor_valid(args, c); cursor_advance(args, c)) {
-                const int plane = c.w.seq * args.kv_heads + c.w.kv_head;
-                const int slot = int(c.t % LT::kStages);
-                const uint32_t round = c.t / LT::kStages;
-                const int row0 = row_of_tile(args.map, c.w.tile_first + c.j * world);
-                if (round > 0 && !mbar_wait(&bars->k_empty[slot], (round - 1) & 1, abort_flag, args.status, 1)) break;
-                mbar_expect_tx(&bars->k_full[slot], LT::kTileBytes);
-                for (int b = 0; b < LT::kBlocks; ++b) {
-                    tma_load_3d(k_smem + slot * LT::kTileBytes + b * (kTileKeys * 128), &tmap_k,
-                                &bars->k_full[slot], b * 64, row0, plane);
+            uint32_t t = 0;
+            bool ok = true;
+            for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item)) {
+                const TcItem w = decode_item(args, item);
+                const int plane = w.seq * args.kv_heads + w.kv_head;
+                for (int j = 0; j < w.n_tiles; ++j, ++t) {
+                    const int slot = int(t % LT::kStages);
+                    const uint32_t round = t / LT::kStages;
+                    const int row0 = row_of_tile(args.map, w.tile_first + j * world);
+                    if (round > 0 && !mbar_wait(&bars->k_empty[slot], (round - 1) & 1, abort_flag, args.status, 1)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&bars->k_full[slot], LT::kTileBytes);
+                    for (int b = 0; b < LT::kBlocks; ++b) {
+                        tma_load_3d(k_smem + slot * LT::kTileBytes + b * (kTileKeys * 128), &tmap_k,
+                                    &bars->k_full[slot], b * 64, row0, plane);
+                    }
+                    if (round > 0 && !mbar_wait(&bars->v_empty[slot], (round - 1) & 1, abort_flag, args.status, 2)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&bars->v_full[slot], LT::kTileBytes);
+                    for (int b = 0; b < LT::kBlocks; ++b) {
+                        tma_load_3d(v_smem + slot * LT::kTileBytes + b * (kTileKeys * 128), &tmap_v,
+                                    &bars->v_full[slot], b * 64, row0, plane);
+                    }
+                    TC_TRACE(2);
                 }
-                if (round > 0 && !mbar_wait(&bars->v_empty[slot], (round - 1) & 1, abort_flag, args.status, 2)) break;
-                mbar_expect_tx(&bars->v_full[slot], LT::kTileBytes);
-                for (int b = 0; b < LT::kBlocks; ++b) {
-                    tma_load_3d(v_smem + slot * LT::kTileBytes + b * (kTileKeys * 128), &tmap_v,
-                                &bars->v_full[slot], b * 64, row0, plane);
-                }
-                TC_TRACE(2);
             }
         }
     } else if (warp == 1) {
-        // ===== MMA issuer: S runs up to two tiles ahead of P V, across item boundaries too =====
+        // ===== MMA issuer: S(t + 1) is issued before P(t) is awaited, across item boundaries too =====
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc(kTileKeys, false);
             constexpr uint32_t idesc_pv = instr_desc(D, true);
             constexpr uint32_t idesc_sum = instr_desc(16, false);
             const uint64_t ones_desc = smem_desc(smem_u32(ones_smem), 16);
-            // S = Q K^T of the tile under cursor `c`.
-            auto issue_qk = [&](const TcCursor& c) -> bool {
-                const int slot = int(c.t % LT::kStages);
-                const int qb = int(c.it & 1);
-                const int sb = int(c.t & 1);
-                if (c.j == 0 && !mbar_wait(&bars->q_full[qb], (c.it >> 1) & 1, abort_flag, args.status, 4)) return false;
+            // S = Q K^T of stream tile t; `it` is the ordinal of its item, `last` marks its item's last tile.
+            auto issue_qk = [&](uint32_t t, uint32_t it, bool first, bool last) -> bool {
+                const int slot = int(t % LT::kStages);
+                const int qb = int(it & 1);
+                if (first && !mbar_wait(&bars->q_full[qb], (it >> 1) & 1, abort_flag, args.status, 4)) return false;
                 TC_TRACE(3);
-                if (!mbar_wait(&bars->k_full[slot], (c.t / LT::kStages) & 1, abort_flag, args.status, 3)) return false;
+                if (!mbar_wait(&bars->k_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 3)) return false;
                 TC_TRACE(4);
                 tc_fence_after();
                 const uint32_t q_addr = smem_u32(q_smem + qb * LT::kQBytes);
                 const uint32_t k_addr = smem_u32(k_smem + slot * LT::kTileBytes);
-                const uint32_t s_tmem = tmem + sb * kTileKeys;
+                const uint32_t s_tmem = tmem + ((t & 1) ? LT::kSCol1 : LT::kSCol0);
                 #pragma unroll
                 for (int b = 0; b < LT::kBlocks; ++b) {
                     #pragma unroll
@@ -322,97 +309,192 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     }
                 }
                 tc_commit(&bars->k_empty[slot]);
-                tc_commit(&bars->s_full[sb]);
-                if (c.j + 1 == c.w.n_tiles) tc_commit(&bars->q_empty[qb]);   // the item's Q tile was read for the last time
+                tc_commit(&bars->s_full[t & 1]);
+                if (last) tc_commit(&bars->q_empty[qb]);        // the item's Q tile has been read for the last time
                 return true;
             };
-            TcCursor ahead = cursor_begin(args);          // next tile whose S is to be issued
-            bool ok = true;
-            for (TcCursor c = cursor_begin(args); ok && cursor_valid(args, c); cursor_advance(args, c)) {
-                // S of tile t + 1 goes to the buffer tile t - 1 used; its P V is already queued.  The
-                // look-ahead never waits for a Q tile beyond the next item's: that one is staged only
-                // after the fold warpgroup has seen this item's outputs.
-                while (ok && cursor_valid(args, ahead) && ahead.t < c.t + 2 && ahead.it <= c.it + 1) {
-                    ok = issue_qk(ahead);
-                    cursor_advance(args, ahead);
-                }
-                if (!ok) break;
-                const int slot = int(c.t % LT::kStages);
-                const int sb = int(c.t & 1);
-                if (!mbar_wait(&bars->p_full[sb], (c.t >> 1) & 1, abort_flag, args.status, 5)) break;
-                if (!mbar_wait(&bars->v_full[slot], (c.t / LT::kStages) & 1, abort_flag, args.status, 6)) break;
-                if (c.t >= 2 && !mbar_wait(&bars->o_free[sb], ((c.t >> 1) - 1) & 1, abort_flag, args.status, 7)) break;
-                tc_fence_after();
-                const uint32_t v_addr = smem_u32(v_smem + slot * LT::kTileBytes);
-                const uint32_t p_tmem = tmem + sb * kTileKeys;
-                const uint32_t o_tmem = tmem + LT::kOCol0 + sb * LT::kOStride;
-                #pragma unroll
-                for (int ks = 0; ks < kTileKeys / 16; ++ks) {
-                    mma_ts(o_tmem, p_tmem + ks * 8, smem_desc(v_addr + ks * 2048, kTileKeys * 128), idesc_pv,
-                           ks != 0 ? 1u : 0u);
-                }
-                if (LT::kSumOnTensor) {
-                    // Row sums of P on the tensor core: P x ones, 16 identical columns beside O.
+            uint32_t t = 0, it = 0;
+            int item = first_item(args);
+            bool ok = item < args.n_items;
+            TcItem w{};
+            if (ok) {
+                w = decode_item(args, item);
+                ok = issue_qk(0, 0, true, w.n_tiles == 1);
+            }
+            while (ok) {
+                int nxt = item;
+                TcItem wn = w;
+                for (int j = 0; ok && j < w.n_tiles; ++j, ++t) {
+                    if (j + 1 < w.n_tiles) {
+                        ok = issue_qk(t + 1, it, false, j + 2 == w.n_tiles);
+                    } else {
+                        nxt = next_item(args, item);
+                        if (nxt < args.n_items) {
+                            wn = decode_item(args, nxt);
+                            ok = issue_qk(t + 1, it + 1, true, wn.n_tiles == 1);
+                        }
+                    }
+                    if (!ok) break;
+                    const int slot = int(t % LT::kStages);
+                    const int ob = int(t % LT::kOBufs);
+                    if (!mbar_wait(&bars->p_full[t & 1], (t >> 1) & 1, abort_flag, args.status, 5)) { ok = false; break; }
+                    if (!mbar_wait(&bars->v_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 6)) { ok = false; break; }
+                    if (t >= LT::kOBufs &&
+                        !mbar_wait(&bars->o_free[ob], (t / LT::kOBufs - 1) & 1, abort_flag, args.status, 7)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t v_addr = smem_u32(v_smem + slot * LT::kTileBytes);
+                    const uint32_t p_tmem = tmem + ((t & 1) ? LT::kSCol1 : LT::kSCol0);
+                    const uint32_t o_tmem = tmem + LT::kOCol0 + ob * LT::kOStride;
                     #pragma unroll
                     for (int ks = 0; ks < kTileKeys / 16; ++ks) {
-                        mma_ts(o_tmem + D, p_tmem + ks * 8, ones_desc, idesc_sum, ks != 0 ? 1u : 0u);
+                        mma_ts(o_tmem, p_tmem + ks * 8, smem_desc(v_addr + ks * 2048, kTileKeys * 128), idesc_pv,
+                               ks != 0 ? 1u : 0u);
                     }
+                    if (LT::kSumOnTensor) {
+                        // Row sums of P on the tensor core: P x ones, 16 identical columns beside O.
+                        #pragma unroll
+                        for (int ks = 0; ks < kTileKeys / 16; ++ks) {
+                            mma_ts(o_tmem + D, p_tmem + ks * 8, ones_desc, idesc_sum, ks != 0 ? 1u : 0u);
+                        }
+                    }
+                    tc_commit(&bars->v_empty[slot]);
+                    tc_commit(&bars->o_full[ob]);
                 }
-                tc_commit(&bars->v_empty[slot]);
-                tc_commit(&bars->o_full[sb]);
+                if (!ok || nxt >= args.n_items || nxt == item) break;
+                item = nxt;
+                w = wn;
+                ++it;
             }
         }
     }
     } else if (wg == 1 || wg == 2) {
-        // ===== softmax: warpgroup 1 takes the even tiles of the stream, warpgroup 2 the odd ones, so
-        // one group's exp2 phase overlaps the other's loads and maximum.  Thread = row. =====
+        // ===== softmax: two threads per row, one per 64-column half of the tile =====
         reg_dealloc<112>();
-        const int parity = wg - 1;
+        const int half = wg - 1;                             // 0: columns 0-63, 1: columns 64-127
         const int quad = warp & 3;                           // the TMEM lane quadrant this warp may touch
         const int row = quad * 32 + lane;
         const int t_local = row >> args.log_group;
         const uint32_t lane_base = uint32_t(quad * 32) << 16;
         const float neg_inf = __int_as_float(0xff800000);
+        uint32_t t = 0, xuse = 0;
+        bool ok = true;
         TC_LAP_DECL
-        for (TcCursor c = cursor_begin(args); cursor_valid(args, c); cursor_advance(args, c)) {
-            if (int(c.t & 1) != parity) continue;
-            const bool valid = t_local < c.w.valid_tokens;
-            const bool warp_has_rows = quad * 32 < (c.w.valid_tokens << args.log_group);   // warp-uniform
-            const int pos = valid ? c.w.first_pos + t_local : -1;
+        for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item)) {
+            const TcItem w = decode_item(args, item);
+            const bool valid = t_local < w.valid_tokens;
+            const bool warp_has_rows = quad * 32 < (w.valid_tokens << args.log_group);   // warp-uniform
+            const int pos = valid ? w.first_pos + t_local : -1;
             const int lo = args.window > 0 ? max(0, pos - args.window + 1) : 0;
-            const int sb = int(c.t & 1);
-            TC_LAP(5)
-            if (!mbar_wait(&bars->s_full[sb], (c.t >> 1) & 1, abort_flag, args.status, 8)) break;
-            TC_LAP(0)
-            if (threadIdx.x == 128) TC_TRACE(5);
-            tc_fence_after();
-            if (!warp_has_rows) {
-                // No query row lives in this quadrant: its P rows stay whatever they were and the
-                // O rows they produce are never read (rows are independent).
-                tc_fence_before();
-                mbar_arrive(&bars->p_full[sb]);
-                continue;
-            }
-            const uint32_t s_tmem = tmem + lane_base + sb * kTileKeys;
-            const int key0 = (c.w.tile_first + c.j * world) * kTileKeys;
-            const int c_lo = lo - key0;                      // visible columns: [c_lo, c_hi]
-            const int c_hi = pos - key0;
-            const bool full = c_lo <= 0 && c_hi >= kTileKeys - 1;
-            // Pass 1: the row maximum, 64 columns at a time (exact under any association).
-            float m = neg_inf;
-            #pragma unroll
-            for (int hb = 0; hb < 2; ++hb) {
-                uint32_t s[2][32];
-                HC_TMEM_LD32(s_tmem + hb * 64, s[0]);
-                HC_TMEM_LD32(s_tmem + hb * 64 + 32, s[1]);
-                tc_wait_ld();
-                if (!full) {
+            for (int j = 0; j < w.n_tiles; ++j, ++t) {
+                const int sb = int(t & 1);
+                TC_LAP(5)
+                if (!mbar_wait(&bars->s_full[sb], (t >> 1) & 1, abort_flag, args.status, 8)) { ok = false; break; }
+                TC_LAP(0)
+                if (threadIdx.x == 128) TC_TRACE(5);
+                tc_fence_after();
+                if (!warp_has_rows) {
+                    // No query row lives in this quadrant: its P rows stay whatever they were and the
+                    // O rows they produce are never read (rows are independent).
+                    tc_fence_before();
+                    mbar_arrive(&bars->p_full[sb]);
+                    continue;
+                }
+                const uint32_t s_tmem = tmem + lane_base + (sb ? LT::kSCol1 : LT::kSCol0);
+                const int key0 = (w.tile_first + j * world) * kTileKeys + half * 64;
+                if (args.decode && LT::kSumOnTensor) {
+                    // Decode has at most 16 real rows, all in quadrant 0 and all at one position.  The
+                    // 16x256b shape spreads each row over four threads, so the warp computes 16 x 64
+                    // weights instead of 32 x 64.  Element for element the weights are the ones the
+                    // prefill layout computes; the row sums come from the tensor core either way.
+                    const int q4 = lane & 3;
+                    const int c_lo = max(0, w.first_pos - (args.window > 0 ? args.window - 1 : w.first_pos)) - key0;
+                    const int c_hi = w.first_pos - key0;
+                    const bool upper = G > 8;                // rows 8-15 hold heads only when the group is 16
+                    uint32_t v[32];
+                    HC_TMEM_LD_16x256b_x8(s_tmem + half * 64, v);
+                    tc_wait_ld();
+                    float mrow[2] = {neg_inf, neg_inf};
                     #pragma unroll
-                    for (int idx = 0; idx < 64; ++idx) {
-                        const int col = hb * 64 + idx;
-                        if (col < c_lo || col > c_hi) s[idx >> 5][idx & 31] = __float_as_uint(neg_inf);
+                    for (int n = 0; n < 8; ++n) {
+                        #pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int col = 8 * n + 2 * q4 + e;
+                            const bool visible = col >= c_lo && col <= c_hi;
+                            #pragma unroll
+                            for (int rs = 0; rs < 2; ++rs) {
+                                if (!visible) v[4 * n + 2 * rs + e] = __float_as_uint(neg_inf);
+                                mrow[rs] = fmaxf(mrow[rs], __uint_as_float(v[4 * n + 2 * rs + e]));
+                            }
+                        }
+                    }
+                    #pragma unroll
+                    for (int rs = 0; rs < 2; ++rs) {
+                        mrow[rs] = fmaxf(mrow[rs], __shfl_xor_sync(0xffffffffu, mrow[rs], 1));
+                        mrow[rs] = fmaxf(mrow[rs], __shfl_xor_sync(0xffffffffu, mrow[rs], 2));
+                        if (q4 == 0) bars->xmax[sb][half][(lane >> 2) + 8 * rs] = mrow[rs];
+                    }
+                    mbar_arrive(&bars->x_bar[quad]);
+                    if (!mbar_wait(&bars->x_bar[quad], xuse & 1, abort_flag, args.status, 11)) { ok = false; break; }
+                    ++xuse;
+                    uint32_t pk[2][8];                       // pk[rs][n]: P column 4n + q4 of row lane/4 + 8rs
+                    #pragma unroll
+                    for (int rs = 0; rs < 2; ++rs) {
+                        const int r = (lane >> 2) + 8 * rs;
+                        const float m = fmaxf(mrow[rs], bars->xmax[sb][half ^ 1][r]);
+                        const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
+                        if (half == 0 && q4 == 0) bars->mm[t & 3][r] = __fmul_rn(m, args.c);
+                        #pragma unroll
+                        for (int n = 0; n < 8; ++n) {
+                            if (rs == 0 || upper) {
+                                const float e0 = tile_weight_raw(__uint_as_float(v[4 * n + 2 * rs]), neg_mc, args.c);
+                                const float e1 = tile_weight_raw(__uint_as_float(v[4 * n + 2 * rs + 1]), neg_mc, args.c);
+                                pk[rs][n] = pack_bf16x2(e0, e1);
+                            } else {
+                                pk[rs][n] = 0u;
+                            }
+                        }
+                    }
+                    // The store shape wants thread q4 to hold P columns 8m + 2 q4 + {0, 1}; it computed
+                    // columns 4n + q4.  Column 8m + 2 q4 + e lives in thread (2 q4 + e) % 4 as its
+                    // element n = 2m + (q4 >= 2).
+                    uint32_t st[16];
+                    #pragma unroll
+                    for (int mcol = 0; mcol < 4; ++mcol) {
+                        #pragma unroll
+                        for (int rs = 0; rs < 2; ++rs) {
+                            #pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int src = (lane & ~3) | ((2 * q4 + e) & 3);
+                                const uint32_t x0 = __shfl_sync(0xffffffffu, pk[rs][2 * mcol], src);
+                                const uint32_t x1 = __shfl_sync(0xffffffffu, pk[rs][2 * mcol + 1], src);
+                                st[4 * mcol + 2 * rs + e] = q4 >= 2 ? x1 : x0;
+                            }
+                        }
+                    }
+                    HC_TMEM_ST_16x256b_x4(s_tmem + half * 32, st);
+                    tc_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(&bars->p_full[sb]);
+                    continue;
+                }
+                const int c_lo = lo - key0;                  // visible columns of this half: [c_lo, c_hi]
+                const int c_hi = pos - key0;
+                uint32_t s[2][32];
+                HC_TMEM_LD32(s_tmem + half * 64, s[0]);
+                HC_TMEM_LD32(s_tmem + half * 64 + 32, s[1]);
+                tc_wait_ld();
+                TC_LAP(1)
+                if (!(c_lo <= 0 && c_hi >= 63)) {
+                    #pragma unroll
+                    for (int q2 = 0; q2 < 2; ++q2) {
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int col = q2 * 32 + i;
+                            if (col < c_lo || col > c_hi) s[q2][i] = __float_as_uint(neg_inf);
+                        }
                     }
                 }
+                // Maximum of this half (exact under any association), then of the row through shared memory.
                 float mx[4];
                 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
@@ -424,42 +506,35 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     }
                     mx[u] = fmaxf(acc, __uint_as_float(s[1][28 + u]));
                 }
-                m = fmax3(m, fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            }
-            const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
-            TC_LAP(2)
-            // Pass 2: weights, 64 columns at a time; P overwrites the S columns already consumed.
-            float sum = 0.0f;
-            #pragma unroll
-            for (int hb = 0; hb < 2; ++hb) {
-                uint32_t s[2][32];
-                HC_TMEM_LD32(s_tmem + hb * 64, s[0]);
-                HC_TMEM_LD32(s_tmem + hb * 64 + 32, s[1]);
-                tc_wait_ld();
-                if (!full) {
-                    #pragma unroll
-                    for (int idx = 0; idx < 64; ++idx) {
-                        const int col = hb * 64 + idx;
-                        if (col < c_lo || col > c_hi) s[idx >> 5][idx & 31] = __float_as_uint(neg_inf);
-                    }
-                }
+                const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                bars->xmax[sb][half][row] = m_half;
+                mbar_arrive(&bars->x_bar[quad]);             // the two warps that share this quadrant
+                if (!mbar_wait(&bars->x_bar[quad], xuse & 1, abort_flag, args.status, 11)) { ok = false; break; }
+                ++xuse;
+                const float m = fmaxf(m_half, bars->xmax[sb][half ^ 1][row]);
+                const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
+                TC_LAP(2)
+                uint32_t packed[32];
                 #pragma unroll
                 for (int q2 = 0; q2 < 2; ++q2) {
-                    uint32_t packed[16];
                     #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const float e0 = tile_weight_raw(__uint_as_float(s[q2][2 * i]), neg_mc, args.c);
                         const float e1 = tile_weight_raw(__uint_as_float(s[q2][2 * i + 1]), neg_mc, args.c);
-                        packed[i] = pack_bf16x2(e0, e1);
+                        packed[q2 * 16 + i] = pack_bf16x2(e0, e1);
                     }
-                    HC_TMEM_ST16(s_tmem + hb * 32 + q2 * 16, packed);
-                    if (!LT::kSumOnTensor) {
-                        // Group of 32 columns by the butterfly tree (i with i + 16, + 8, + 4, + 2, + 1);
-                        // the four groups of the row are then added in order.
+                    HC_TMEM_ST16(s_tmem + half * 32 + q2 * 16, (&packed[q2 * 16]));
+                }
+                if (!LT::kSumOnTensor) {
+                    // Sum of this half's 64 weights: two groups of 32, each by the butterfly tree
+                    // (i with i + 16, then + 8, + 4, + 2, + 1), then the two groups added.
+                    float part[2];
+                    #pragma unroll
+                    for (int q2 = 0; q2 < 2; ++q2) {
                         float a[16];
                         #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            const uint32_t lo_word = packed[i >> 1], hi_word = packed[(i + 16) >> 1];
+                            const uint32_t lo_word = packed[q2 * 16 + (i >> 1)], hi_word = packed[q2 * 16 + ((i + 16) >> 1)];
                             const float x = __uint_as_float((i & 1) ? (lo_word & 0xffff0000u) : (lo_word << 16));
                             const float y = __uint_as_float((i & 1) ? (hi_word & 0xffff0000u) : (hi_word << 16));
                             a[i] = __fadd_rn(x, y);
@@ -470,19 +545,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         for (int i = 0; i < 4; ++i) a[i] = __fadd_rn(a[i], a[i + 4]);
                         a[0] = __fadd_rn(a[0], a[2]);
                         a[1] = __fadd_rn(a[1], a[3]);
-                        const float group = __fadd_rn(a[0], a[1]);
-                        sum = (hb == 0 && q2 == 0) ? group : __fadd_rn(sum, group);
+                        part[q2] = __fadd_rn(a[0], a[1]);
                     }
+                    bars->l[t & 3][half][row] = __fadd_rn(part[0], part[1]);
                 }
+                if (half == 0) bars->mm[t & 3][row] = __fmul_rn(m, args.c);
+                TC_LAP(3)
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(&bars->p_full[sb]);
+                TC_LAP(4)
+                if (threadIdx.x == 128) TC_TRACE(6);
             }
-            bars->mm[c.t & 3][row] = __fmul_rn(m, args.c);
-            if (!LT::kSumOnTensor) bars->l[c.t & 3][row] = sum;
-            TC_LAP(3)
-            tc_wait_st();
-            tc_fence_before();
-            mbar_arrive(&bars->p_full[sb]);
-            TC_LAP(4)
-            if (threadIdx.x == 128) TC_TRACE(6);
         }
         if (threadIdx.x == 128) { TC_LAP_STORE(1) }
     } else {
@@ -509,6 +583,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             }
             fence_proxy_async();
             mbar_arrive(&bars->q_full[qb]);
+        };
+        // The tile's row sum: from the tensor core (column D of the O buffer) or the two halves' sums.
+        auto tile_sum = [&](uint32_t o_tmem, uint32_t t) -> float {
+            if (LT::kSumOnTensor) {
+                const uint32_t bits = tmem_ld1(o_tmem + D);
+                tc_wait_ld();
+                return __uint_as_float(bits);
+            }
+            return __fadd_rn(bars->l[t & 3][0][row], bars->l[t & 3][1][row]);
         };
         uint32_t t = 0, it = 0;
         bool ok = true;
@@ -542,9 +625,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             #pragma unroll
             for (int i = 0; i < D; ++i) A[i] = 0.0f;
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
-                const int ob = int(t & 1);
-                const uint32_t o_tmem = tmem + lane_base + LT::kOCol0 + ob * LT::kOStride;
-                if (!mbar_wait(&bars->o_full[ob], (t >> 1) & 1, abort_flag, args.status, 9)) { ok = false; break; }
+                const int ob = int(t % LT::kOBufs);
+                if (!mbar_wait(&bars->o_full[ob], (t / LT::kOBufs) & 1, abort_flag, args.status, 9)) { ok = false; break; }
                 if (threadIdx.x == 384) TC_TRACE(7);
                 tc_fence_after();
                 if (!warp_has_rows) {
@@ -552,16 +634,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     mbar_arrive(&bars->o_free[ob]);
                     continue;
                 }
-                // The tile's row sum: column D of the O buffer (tensor core) or the softmax thread's sum.
-                float l_tile;
-                if (LT::kSumOnTensor) {
-                    const uint32_t bits = tmem_ld1(o_tmem + D);
-                    tc_wait_ld();
-                    l_tile = __uint_as_float(bits);
-                } else {
-                    l_tile = bars->l[t & 3][row];
-                }
-                const float mm_tile = bars->mm[t & 3][row];
+                const uint32_t o_tmem = tmem + lane_base + LT::kOCol0 + ob * LT::kOStride;
+                const float l_tile = tile_sum(o_tmem, t);
                 if (args.decode) {
                     // Split decode: the tile's partial goes to the workspace; merge_tiles_kernel folds.
                     const size_t prow = (size_t(w.row0) * args.q_heads + head) * args.part_tiles + (w.ordinal0 + j);
@@ -588,13 +662,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         }
                     }
                     if (valid) {
-                        args.part_ml[prow * 2] = mm_tile;
+                        args.part_ml[prow * 2] = bars->mm[t & 3][row];
                         args.part_ml[prow * 2 + 1] = l_tile;
                     }
                     continue;
                 }
                 float Mn, a, b;
-                fold_coefficients(M, mm_tile, Mn, a, b);
+                fold_coefficients(M, bars->mm[t & 3][row], Mn, a, b);
                 L = __fmaf_rn(L, a, __fmul_rn(l_tile, b));
                 M = Mn;
                 #pragma unroll

@@ -140,6 +140,30 @@ __device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
           "=r"(v[29]), "=r"(v[30]), "=r"(v[31])                                                             \
         : "r"(taddr) : "memory")
 
+// 16 lanes x 256 bits, eight times along the columns: 16 rows x 64 columns.  Thread i of the warp
+// gets, for n = 0..7, v[4n], v[4n+1] = row i/4, columns 8n + 2(i%4) + {0, 1} and v[4n+2], v[4n+3] =
+// row i/4 + 8, the same columns (the layout of an m16n8 accumulator fragment).
+#define HC_TMEM_LD_16x256b_x8(taddr, v)                                                                     \
+    asm volatile(                                                                                           \
+        "tcgen05.ld.sync.aligned.16x256b.x8.b32 "                                                           \
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                          \
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"          \
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),  \
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),         \
+          "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),       \
+          "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),       \
+          "=r"(v[29]), "=r"(v[30]), "=r"(v[31])                                                             \
+        : "r"(taddr) : "memory")
+
+// The matching store, four times along the columns: 16 rows x 32 columns.
+#define HC_TMEM_ST_16x256b_x4(taddr, v)                                                                     \
+    asm volatile(                                                                                           \
+        "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], "                                                     \
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"                          \
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),         \
+          "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),     \
+          "r"(v[15]) : "memory")
+
 #define HC_TMEM_ST16(taddr, v)                                                                              \
     asm volatile(                                                                                           \
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "                                                     \
