@@ -295,6 +295,40 @@ def run_cuda(args):
               "frac_of_measured": dec_gbs / (peaks["hbm_gbs"] * world),
               "note": "call = q prologue + split kernel + merge; L2 flushed before each timed call"}
 
+    # The HBM-bound decode case: one batched decode step over 64 ragged sequences (lengths U[1024,
+    # 16384], seed 7; the full-attention layer of configuration C5), KV heads sharded like C2's.
+    # 1.2 GB of K/V per step at one GPU, far beyond L2, so no flush is needed.
+    lens = np.random.default_rng(7).integers(1024, 16385, size=64)
+    big = hb.KVCache(ctx, [dict(q_heads=cfg.q_heads, kv_heads=per, head_dim=d, window=0)], 16384, max_seqs=64)
+    gen = torch.Generator(device="cuda").manual_seed(7 + rank)
+    plain = hb.AttnParams(q_heads=cfg.q_heads, kv_heads=per, head_dim=d, window=0, sm_scale=cfg.scale,
+                          io_dtype=hb.capi.HC_BF16, sinks=params.sinks)
+    for seq, n in enumerate(lens):
+        block = torch.randn(int(n), per, d, device="cuda", generator=gen).to(torch.bfloat16)
+        backend.write_key_value(big, 0, block, block, int(n), 0, plain, seq=seq, stream=stream)
+    torch.cuda.synchronize()
+    bq = torch.randn(64, cfg.q_heads, d, device="cuda", generator=gen).to(torch.bfloat16)
+    bo = torch.empty_like(bq)
+    bpos = [int(n) - 1 for n in lens]
+    big_ms = []
+    for i in range(12):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        backend.attention(big, 0, bq, bo, bpos, plain, seq_ids=list(range(64)), stream=stream)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        if i >= 3:
+            big_ms.append(e0.elapsed_time(e1))
+    ctx.check()
+    big_us = max_over_ranks(statistics.median(big_ms) * 1e3, world)
+    big_bytes = int(lens.sum()) * per * d * 2 * 2
+    big_gbs = big_bytes * world / (big_us * 1e-6) / 1e9
+    decode_large = {"workload": "C5 full-attention layer: 64 ragged sequences (sum of lengths 591950), one decode step",
+                    "us_per_step": big_us, "kv_bytes_per_step": big_bytes * world, "kv_gbs": big_gbs,
+                    "frac_of_8tbs": big_gbs / (8000.0 * world), "frac_of_measured": big_gbs / (peaks["hbm_gbs"] * world),
+                    "note": "call = split kernel + merge, CUDA events; per-GPU peak x n_gpus in the fractions"}
+    big.close()
+
     # End to end: the same prefill through hc_layer_step_host with pinned host buffers.
     host = {name: dev[name].cpu().pin_memory() for name in ("q", "k", "v")}
     host_out = torch.zeros_like(dev["out"], device="cpu").pin_memory()
@@ -339,7 +373,7 @@ def run_cuda(args):
                                    "(KV append + attention), then one decode step at context 4096",
                        "kv_heads_per_gpu": per, "parallelism": f"kv-head shard x{world}",
                        "l2": f"{n_sets} rotating copies of the prompt's buffers (> 2x L2); decode flushes L2"},
-            "roofline": roofline, "decode": decode, "e2e": e2e, "cpu_baseline": cpu, "clocks": clocks,
+            "roofline": roofline, "decode": decode, "decode_large": decode_large, "e2e": e2e, "cpu_baseline": cpu, "clocks": clocks,
             "gpu_launches": launches,
             "prefill_tflops_whole_step": wl.prefill_flops(cfg) * world / (ms_per_step * 1e-3) / 1e12,
         }
