@@ -11,13 +11,20 @@
 // TMA ring, tensor memory and barriers across items, so one item's ramp-up hides behind the
 // previous item's tail.
 //
-//   warp 0      producer: TMA loads of K and V tiles (128 keys x d, 128-byte swizzle) into a ring
-//   warp 1      MMA issuer: S = Q K^T (A, B from shared memory), O_j = P V (A = P from tensor memory)
-//   warps 2-5   softmax: S from tensor memory, causal / window mask, row maximum, P = bf16(exp2(..)),
-//               row sum, P back into tensor memory over S
-//   warps 6-9   fold: stages the next item's Q tile in shared memory; O_j from tensor memory folded
-//               into the row's running (M, L, A) in registers (prefill) or written out as the
-//               tile's partial (decode); the epilogue (divide, gate, store)
+//   warpgroup 0 (warps 0-3)    warp 0 producer: TMA loads of K and V tiles (128 keys x d, 128-byte
+//                              swizzle) into a ring; warp 1 MMA issuer: S = Q K^T (A, B from shared
+//                              memory), O_j = P V (A = P from tensor memory) and, for d = 64, the row
+//                              sums P x ones; warps 2-3 idle
+//   warpgroups 1-2 (warps 4-11) softmax, two threads per row: group 1 takes columns 0-63 of the S
+//                              tile, group 2 columns 64-127.  S from tensor memory, causal / window
+//                              mask, the row maximum exchanged through shared memory,
+//                              P = bf16(exp2(..)) back into tensor memory over S.  In decode the 16
+//                              real rows are read with the 16x256b shape, four threads per row.
+//   warpgroup 3 (warps 12-15)   fold: stages the next item's Q tile in shared memory; O_j from tensor
+//                              memory folded into the row's running (M, L, A) in registers (prefill)
+//                              or written out as the tile's partial (decode); the epilogue
+//
+// Registers are moved between the warpgroups with setmaxnreg (48 / 112 / 112 / 232 per thread).
 //
 // The arithmetic is the canonical tile-partial + fold of common.cuh: every key tile yields an
 // independent partial with its own maximum and the partials are folded in ascending tile order
@@ -32,38 +39,11 @@
 #include <algorithm>
 
 #include "internal.hpp"
+#include "tc_common.cuh"
 #include "tc_ptx.cuh"
 
 namespace hc {
 namespace {
-
-struct TcArgs {
-    const uint16_t* q;        // bf16 [rows][q_heads][d], prepared
-    int tokens;               // prefill: tokens of the chunk
-    int first_position;
-    int q_heads;
-    int kv_heads;
-    int log_group;
-    int window;
-    float c;
-    const uint16_t* sinks;
-    int count_sink;
-    int seq;
-    RowMap map;
-    EpilogueArgs ep;
-    int* status;
-    int n_items;              // work items in the list
-    int mtiles;               // prefill: row tiles per kv head
-    // Decode (split over key tiles): one query token per batch entry; an item is a run of
-    // `tiles_per_item` consecutive key tiles of one (sequence, kv head) whose partials it writes.
-    int decode;
-    int chunks;               // decode: items per (sequence, kv head)
-    int tiles_per_item;
-    float* part_o;            // fp32 [rows][part_tiles][d]
-    float* part_ml;           // fp32 [rows][part_tiles][2]
-    int part_tiles;
-    BatchMeta meta;
-};
 
 template <int D>
 struct TcLayout {
@@ -95,77 +75,6 @@ struct TcBarriers {
 };
 
 // One unit of work of a CTA.
-struct TcItem {
-    int kv_head;
-    int seq;
-    int row0;          // first row of q / out (token index of the chunk, or batch entry)
-    int valid_tokens;  // query tokens in this row tile
-    int first_pos;     // position of the first query token
-    int tile_first;    // absolute index of the first key tile
-    int n_tiles;       // key tiles to visit (stride `world` apart); <= 0: nothing to do
-    int ordinal0;      // decode: ordinal of the first tile among the row's tiles
-};
-
-__device__ __forceinline__ TcItem decode_item(const TcArgs& args, int index) {
-    TcItem w;
-    const int tokens_per_tile = kRows >> args.log_group;
-    int chunk = 0;
-    if (args.decode) {
-        chunk = index % args.chunks;
-        const int rest = index / args.chunks;
-        w.kv_head = rest % args.kv_heads;
-        const int b = rest / args.kv_heads;
-        w.row0 = b;
-        w.valid_tokens = 1;
-        w.first_pos = args.meta.pos[b];
-        w.seq = args.meta.seq[b];
-    } else {
-        // Longest key ranges first: descending row tile, the kv heads of one row tile adjacent.
-        w.kv_head = index % args.kv_heads;
-        const int mtile = args.mtiles - 1 - index / args.kv_heads;
-        w.row0 = mtile * tokens_per_tile;
-        w.valid_tokens = min(tokens_per_tile, args.tokens - w.row0);
-        w.first_pos = args.first_position + w.row0;
-        w.seq = args.seq;
-    }
-    const int last_pos = w.first_pos + w.valid_tokens - 1;
-    const int lo_first = args.window > 0 ? max(0, w.first_pos - args.window + 1) : 0;
-    const int world = max(args.map.world, 1);
-    int tile_first = lo_first / kTileKeys;
-    const int tile_last = last_pos / kTileKeys;
-    if (world > 1) tile_first += ((args.map.rank - tile_first % world) + world) % world;
-    int n_tiles = tile_first > tile_last ? 0 : (tile_last - tile_first) / world + 1;
-    w.ordinal0 = 0;
-    if (args.decode) {
-        w.ordinal0 = chunk * args.tiles_per_item;
-        tile_first += w.ordinal0 * world;
-        n_tiles = min(args.tiles_per_item, n_tiles - w.ordinal0);
-    }
-    w.tile_first = tile_first;
-    w.n_tiles = n_tiles;
-    return w;
-}
-
-// The next item of this CTA's list that has work, or n_items.
-__device__ __forceinline__ int next_item(const TcArgs& args, int index) {
-    for (index += gridDim.x; index < args.n_items; index += gridDim.x) {
-        if (decode_item(args, index).n_tiles > 0) return index;
-    }
-    return args.n_items;
-}
-__device__ __forceinline__ int first_item(const TcArgs& args) {
-    int index = blockIdx.x;
-    if (index < args.n_items && decode_item(args, index).n_tiles > 0) return index;
-    return index < args.n_items ? next_item(args, index) : args.n_items;
-}
-
-// bf16x2 of two softmax weights: `lo` in the low half (the earlier key), `hi` in the high half.
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    uint32_t packed;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
-    return packed;
-}
-
 // Optional timeline for bring-up builds (-DHC_TC_TRACE): nanosecond stamps of a few events per CTA.
 #ifdef HC_TC_TRACE
 __device__ unsigned long long hc_tc_trace[256 * 16 * 4];
@@ -413,68 +322,74 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     uint32_t v[32];
                     HC_TMEM_LD_16x256b_x8(s_tmem + half * 64, v);
                     tc_wait_ld();
-                    float mrow[2] = {neg_inf, neg_inf};
-                    #pragma unroll
-                    for (int n = 0; n < 8; ++n) {
+                    TC_LAP(1)
+                    if (!(c_lo <= 0 && c_hi >= 63)) {
                         #pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int col = 8 * n + 2 * q4 + e;
-                            const bool visible = col >= c_lo && col <= c_hi;
+                        for (int n = 0; n < 8; ++n) {
                             #pragma unroll
-                            for (int rs = 0; rs < 2; ++rs) {
-                                if (!visible) v[4 * n + 2 * rs + e] = __float_as_uint(neg_inf);
-                                mrow[rs] = fmaxf(mrow[rs], __uint_as_float(v[4 * n + 2 * rs + e]));
+                            for (int e = 0; e < 2; ++e) {
+                                const int col = 8 * n + 2 * q4 + e;
+                                if (col < c_lo || col > c_hi) {
+                                    v[4 * n + e] = __float_as_uint(neg_inf);
+                                    v[4 * n + 2 + e] = __float_as_uint(neg_inf);
+                                }
                             }
                         }
                     }
+                    // Row maxima: this thread's 16 columns, then the four threads of the row, then the
+                    // other half of the tile through shared memory.
+                    float mrow[2] = {neg_inf, neg_inf};
                     #pragma unroll
                     for (int rs = 0; rs < 2; ++rs) {
-                        mrow[rs] = fmaxf(mrow[rs], __shfl_xor_sync(0xffffffffu, mrow[rs], 1));
-                        mrow[rs] = fmaxf(mrow[rs], __shfl_xor_sync(0xffffffffu, mrow[rs], 2));
-                        if (q4 == 0) bars->xmax[sb][half][(lane >> 2) + 8 * rs] = mrow[rs];
+                        if (rs == 0 || upper) {
+                            float m0 = __uint_as_float(v[2 * rs]), m1 = __uint_as_float(v[2 * rs + 1]);
+                            #pragma unroll
+                            for (int n = 1; n < 8; n += 2) {
+                                if (n + 1 < 8) {
+                                    m0 = fmax3(m0, __uint_as_float(v[4 * n + 2 * rs]), __uint_as_float(v[4 * (n + 1) + 2 * rs]));
+                                    m1 = fmax3(m1, __uint_as_float(v[4 * n + 2 * rs + 1]), __uint_as_float(v[4 * (n + 1) + 2 * rs + 1]));
+                                } else {
+                                    m0 = fmaxf(m0, __uint_as_float(v[4 * n + 2 * rs]));
+                                    m1 = fmaxf(m1, __uint_as_float(v[4 * n + 2 * rs + 1]));
+                                }
+                            }
+                            float m = fmaxf(m0, m1);
+                            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                            mrow[rs] = m;
+                            if (q4 == 0) bars->xmax[sb][half][(lane >> 2) + 8 * rs] = m;
+                        }
                     }
+                    TC_LAP(2)
                     mbar_arrive(&bars->x_bar[quad]);
                     if (!mbar_wait(&bars->x_bar[quad], xuse & 1, abort_flag, args.status, 11)) { ok = false; break; }
                     ++xuse;
-                    uint32_t pk[2][8];                       // pk[rs][n]: P column 4n + q4 of row lane/4 + 8rs
-                    #pragma unroll
-                    for (int rs = 0; rs < 2; ++rs) {
-                        const int r = (lane >> 2) + 8 * rs;
-                        const float m = fmaxf(mrow[rs], bars->xmax[sb][half ^ 1][r]);
-                        const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
-                        if (half == 0 && q4 == 0) bars->mm[t & 3][r] = __fmul_rn(m, args.c);
-                        #pragma unroll
-                        for (int n = 0; n < 8; ++n) {
-                            if (rs == 0 || upper) {
-                                const float e0 = tile_weight_raw(__uint_as_float(v[4 * n + 2 * rs]), neg_mc, args.c);
-                                const float e1 = tile_weight_raw(__uint_as_float(v[4 * n + 2 * rs + 1]), neg_mc, args.c);
-                                pk[rs][n] = pack_bf16x2(e0, e1);
-                            } else {
-                                pk[rs][n] = 0u;
-                            }
-                        }
-                    }
-                    // The store shape wants thread q4 to hold P columns 8m + 2 q4 + {0, 1}; it computed
-                    // columns 4n + q4.  Column 8m + 2 q4 + e lives in thread (2 q4 + e) % 4 as its
-                    // element n = 2m + (q4 >= 2).
+                    TC_LAP(4)
+                    // st[2n + rs]: P column 4n + q4 of row lane/4 + 8 rs, the layout of the 16x128b store.
                     uint32_t st[16];
                     #pragma unroll
-                    for (int mcol = 0; mcol < 4; ++mcol) {
-                        #pragma unroll
-                        for (int rs = 0; rs < 2; ++rs) {
+                    for (int rs = 0; rs < 2; ++rs) {
+                        if (rs == 0 || upper) {
+                            const int r = (lane >> 2) + 8 * rs;
+                            const float m = fmaxf(mrow[rs], bars->xmax[sb][half ^ 1][r]);
+                            const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
+                            if (half == 0 && q4 == 0) bars->mm[t & 3][r] = __fmul_rn(m, args.c);
                             #pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-                                const int src = (lane & ~3) | ((2 * q4 + e) & 3);
-                                const uint32_t x0 = __shfl_sync(0xffffffffu, pk[rs][2 * mcol], src);
-                                const uint32_t x1 = __shfl_sync(0xffffffffu, pk[rs][2 * mcol + 1], src);
-                                st[4 * mcol + 2 * rs + e] = q4 >= 2 ? x1 : x0;
+                            for (int n = 0; n < 8; ++n) {
+                                const float e0 = tile_weight_raw(__uint_as_float(v[4 * n + 2 * rs]), neg_mc, args.c);
+                                const float e1 = tile_weight_raw(__uint_as_float(v[4 * n + 2 * rs + 1]), neg_mc, args.c);
+                                st[2 * n + rs] = pack_bf16x2(e0, e1);
                             }
+                        } else {
+                            #pragma unroll
+                            for (int n = 0; n < 8; ++n) st[2 * n + rs] = 0u;
                         }
                     }
-                    HC_TMEM_ST_16x256b_x4(s_tmem + half * 32, st);
+                    HC_TMEM_ST_16x128b_x8(s_tmem + half * 32, st);
                     tc_wait_st();
                     tc_fence_before();
                     mbar_arrive(&bars->p_full[sb]);
+                    TC_LAP(3)
                     continue;
                 }
                 const int c_lo = lo - key0;                  // visible columns of this half: [c_lo, c_hi]
@@ -774,7 +689,7 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-bool dim_ok(int d) { return d == 64 || d == 128; }
+bool dim_ok(int d) { return d == 64 || d == 128 || d == 256; }
 
 }  // namespace
 
@@ -854,7 +769,8 @@ hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_sto
     args.mtiles = (tokens + tokens_per_tile - 1) / tokens_per_tile;
     args.n_items = args.mtiles * shape.kv_heads;
     if (shape.head_dim == 64) return launch_tc<64>(ctx, args, layer, stream);
-    return launch_tc<128>(ctx, args, layer, stream);
+    if (shape.head_dim == 128) return launch_tc<128>(ctx, args, layer, stream);
+    return launch_tc256(ctx, layer.tmap_k, layer.tmap_v, &args, args.n_items, stream);
 }
 
 hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer, const CacheView& cache,
@@ -892,8 +808,9 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
     args.ep = ep;
     args.status = ctx->status_dev;
     args.decode = 1;
-    // Items of consecutive tiles, about eight per CTA so that the static round-robin balances.
-    const long long target = 8LL * std::max(ctx->sm_count, 1);
+    // Items of consecutive tiles, about eight per CTA so that the static round-robin balances.  The
+    // head_dim 256 kernel does not look ahead across items, so it gets about one item per CTA.
+    const long long target = (shape.head_dim == 256 ? 1LL : 8LL) * std::max(ctx->sm_count, 1);
     long long per = (total_tiles * shape.kv_heads + target - 1) / target;
     args.tiles_per_item = int(std::min<long long>(std::max<long long>(per, 1), 64));
     args.part_o = ws.part_o;
@@ -903,7 +820,8 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
     args.chunks = (max_tiles + args.tiles_per_item - 1) / args.tiles_per_item;
     args.n_items = args.chunks * shape.kv_heads * n_seq;
     hc_status st = shape.head_dim == 64 ? launch_tc<64>(ctx, args, layer, stream)
-                                        : launch_tc<128>(ctx, args, layer, stream);
+                   : shape.head_dim == 128 ? launch_tc<128>(ctx, args, layer, stream)
+                   : launch_tc256(ctx, layer.tmap_k, layer.tmap_v, &args, args.n_items, stream);
     if (st != HC_OK) return st;
     return launch_merge(ctx, shape, meta, n_seq, ws, max_tiles, world, cache.map.rank, ep, stream);
 }

@@ -164,6 +164,9 @@ hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_sto
 hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer,
                     const CacheView& cache, const BatchMeta& meta, int n_seq, const uint16_t* q,
                     const Workspace& ws, const EpilogueArgs& ep, cudaStream_t stream);
+// attn_tc256.cu (args_ptr: the TcArgs of tc_common.cuh)
+hc_status launch_tc256(hc_context* ctx, const void* tmap_k, const void* tmap_v, const void* args_ptr,
+                       int n_items, cudaStream_t stream);
 hc_status tc_make_tensor_maps(hc_kv_cache* cache, hc_layer_store& layer);
 void tc_free_tensor_maps(hc_layer_store& layer);
 

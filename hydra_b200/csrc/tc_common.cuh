@@ -1,0 +1,113 @@
+// tc_common.cuh — what the tcgen05 attention kernels share: the kernel arguments, the work-item list a
+// persistent CTA walks, and small helpers.
+#pragma once
+
+#include "internal.hpp"
+#include "tc_ptx.cuh"
+
+namespace hc {
+namespace {
+
+struct TcArgs {
+    const uint16_t* q;        // bf16 [rows][q_heads][d], prepared
+    int tokens;               // prefill: tokens of the chunk
+    int first_position;
+    int q_heads;
+    int kv_heads;
+    int log_group;
+    int window;
+    float c;
+    const uint16_t* sinks;
+    int count_sink;
+    int seq;
+    RowMap map;
+    EpilogueArgs ep;
+    int* status;
+    int n_items;              // work items in the list
+    int mtiles;               // prefill: row tiles per kv head
+    // Decode (split over key tiles): one query token per batch entry; an item is a run of
+    // `tiles_per_item` consecutive key tiles of one (sequence, kv head) whose partials it writes.
+    int decode;
+    int chunks;               // decode: items per (sequence, kv head)
+    int tiles_per_item;
+    float* part_o;            // fp32 [rows][part_tiles][d]
+    float* part_ml;           // fp32 [rows][part_tiles][2]
+    int part_tiles;
+    BatchMeta meta;
+};
+
+
+struct TcItem {
+    int kv_head;
+    int seq;
+    int row0;          // first row of q / out (token index of the chunk, or batch entry)
+    int valid_tokens;  // query tokens in this row tile
+    int first_pos;     // position of the first query token
+    int tile_first;    // absolute index of the first key tile
+    int n_tiles;       // key tiles to visit (stride `world` apart); <= 0: nothing to do
+    int ordinal0;      // decode: ordinal of the first tile among the row's tiles
+};
+
+__device__ __forceinline__ TcItem decode_item(const TcArgs& args, int index) {
+    TcItem w;
+    const int tokens_per_tile = kRows >> args.log_group;
+    int chunk = 0;
+    if (args.decode) {
+        chunk = index % args.chunks;
+        const int rest = index / args.chunks;
+        w.kv_head = rest % args.kv_heads;
+        const int b = rest / args.kv_heads;
+        w.row0 = b;
+        w.valid_tokens = 1;
+        w.first_pos = args.meta.pos[b];
+        w.seq = args.meta.seq[b];
+    } else {
+        // Longest key ranges first: descending row tile, the kv heads of one row tile adjacent.
+        w.kv_head = index % args.kv_heads;
+        const int mtile = args.mtiles - 1 - index / args.kv_heads;
+        w.row0 = mtile * tokens_per_tile;
+        w.valid_tokens = min(tokens_per_tile, args.tokens - w.row0);
+        w.first_pos = args.first_position + w.row0;
+        w.seq = args.seq;
+    }
+    const int last_pos = w.first_pos + w.valid_tokens - 1;
+    const int lo_first = args.window > 0 ? max(0, w.first_pos - args.window + 1) : 0;
+    const int world = max(args.map.world, 1);
+    int tile_first = lo_first / kTileKeys;
+    const int tile_last = last_pos / kTileKeys;
+    if (world > 1) tile_first += ((args.map.rank - tile_first % world) + world) % world;
+    int n_tiles = tile_first > tile_last ? 0 : (tile_last - tile_first) / world + 1;
+    w.ordinal0 = 0;
+    if (args.decode) {
+        w.ordinal0 = chunk * args.tiles_per_item;
+        tile_first += w.ordinal0 * world;
+        n_tiles = min(args.tiles_per_item, n_tiles - w.ordinal0);
+    }
+    w.tile_first = tile_first;
+    w.n_tiles = n_tiles;
+    return w;
+}
+
+// The next item of this CTA's list that has work, or n_items.
+__device__ __forceinline__ int next_item(const TcArgs& args, int index) {
+    for (index += gridDim.x; index < args.n_items; index += gridDim.x) {
+        if (decode_item(args, index).n_tiles > 0) return index;
+    }
+    return args.n_items;
+}
+__device__ __forceinline__ int first_item(const TcArgs& args) {
+    int index = blockIdx.x;
+    if (index < args.n_items && decode_item(args, index).n_tiles > 0) return index;
+    return index < args.n_items ? next_item(args, index) : args.n_items;
+}
+
+// bf16x2 of two softmax weights: `lo` in the low half (the earlier key), `hi` in the high half.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t packed;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+    return packed;
+}
+
+
+}  // namespace
+}  // namespace hc

@@ -38,13 +38,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return done != 0;
 }
+// The same with a suspend-time hint: the hardware may park the warp for up to `ns` nanoseconds
+// instead of returning at once, so a waiting warp does not compete for issue slots.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
+    return done != 0;
+}
 // Bounded wait.  Returns false if the CTA is aborting (this wait or another one ran out of time).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int* status_word, int where) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (;;) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_parked(bar, parity, 2000)) return true;
         if (*abort_flag != 0) return false;
         if (static_cast<unsigned long long>(clock64() - start) > kWaitCycles) {
             *abort_flag = 1;
@@ -155,10 +166,12 @@ __device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
           "=r"(v[29]), "=r"(v[30]), "=r"(v[31])                                                             \
         : "r"(taddr) : "memory")
 
-// The matching store, four times along the columns: 16 rows x 32 columns.
-#define HC_TMEM_ST_16x256b_x4(taddr, v)                                                                     \
+// 16 lanes x 128 bits, eight times along the columns: 16 rows x 32 columns.  Thread i holds, for
+// n = 0..7, v[2n] = row i/4, column 4n + i%4 and v[2n+1] = row i/4 + 8, the same column: the packed
+// bf16 pair of the two fp32 columns the 16x256b load gave that thread.
+#define HC_TMEM_ST_16x128b_x8(taddr, v)                                                                     \
     asm volatile(                                                                                           \
-        "tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], "                                                     \
+        "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], "                                                     \
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"                          \
         ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),         \
           "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]),     \

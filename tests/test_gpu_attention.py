@@ -447,6 +447,8 @@ def test_layer_step_with_host_buffers(hb, ctx):
     dict(q_heads=32, kv_heads=2, d=64, window=200, tokens=520, chunk=256),
     dict(q_heads=16, kv_heads=8, d=128, window=0, tokens=300, chunk=128),
     dict(q_heads=16, kv_heads=2, d=128, window=150, tokens=400, chunk=333),
+    dict(q_heads=16, kv_heads=8, d=256, window=0, tokens=300, chunk=128),
+    dict(q_heads=16, kv_heads=2, d=256, window=140, tokens=420, chunk=333),
 ])
 def test_tensor_path_prefill_and_decode(hb, ctx, case):
     """The tcgen05 kernels against the oracle, against the CUDA-core kernels (tolerance) and
