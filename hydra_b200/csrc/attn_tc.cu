@@ -58,7 +58,7 @@ struct TcLayout {
     static constexpr bool kSumOnTensor = D == 64;
     static constexpr int kOStride = kSumOnTensor ? D + 16 : D;
     static constexpr int kTmemCols = 512;
-    static constexpr int kOnesBytes = 2048;
+    static constexpr int kOnesBytes = kTileKeys * 128;       // a 128-row block of bf16 1.0 (16 KiB)
     static constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + 2 * kStages * kTileBytes + kOnesBytes;
 };
 
@@ -105,7 +105,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     unsigned char* q_smem = base;                                  // two Q tiles
     unsigned char* k_smem = q_smem + 2 * LT::kQBytes;
     unsigned char* v_smem = k_smem + LT::kStages * LT::kTileBytes;
-    unsigned char* ones_smem = v_smem + LT::kStages * LT::kTileBytes;   // 2 KiB of bf16 1.0
+    unsigned char* ones_smem = v_smem + LT::kStages * LT::kTileBytes;   // 128 rows of bf16 1.0
     TcBarriers* bars = reinterpret_cast<TcBarriers*>(ones_smem + LT::kOnesBytes);
 
     const int warp = threadIdx.x >> 5;
@@ -193,9 +193,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         // ===== MMA issuer: S(t + 1) is issued before P(t) is awaited, across item boundaries too =====
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc(kTileKeys, false);
-            constexpr uint32_t idesc_pv = instr_desc(D, true);
-            constexpr uint32_t idesc_sum = instr_desc(16, false);
-            const uint64_t ones_desc = smem_desc(smem_u32(ones_smem), 16);
+            // With the row sums on the tensor core, P V and P x ones are one instruction: the B operand
+            // is the V tile (64 columns) followed by a block of ones that the descriptor's
+            // column-block stride points at, so O gets 16 more columns, each the row's sum.
+            constexpr uint32_t idesc_pv = instr_desc(LT::kSumOnTensor ? D + 16 : D, true);
+            const uint32_t ones_addr = smem_u32(ones_smem);
+            const uint32_t v_base = smem_u32(v_smem);
+            const uint64_t q_desc0 = smem_desc(smem_u32(q_smem), 16);
+            const uint64_t k_desc0 = smem_desc(smem_u32(k_smem), 16);
             // S = Q K^T of stream tile t; `it` is the ordinal of its item, `last` marks its item's last tile.
             auto issue_qk = [&](uint32_t t, uint32_t it, bool first, bool last) -> bool {
                 const int slot = int(t % LT::kStages);
@@ -205,16 +210,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 if (!mbar_wait(&bars->k_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 3)) return false;
                 TC_TRACE(4);
                 tc_fence_after();
-                const uint32_t q_addr = smem_u32(q_smem + qb * LT::kQBytes);
-                const uint32_t k_addr = smem_u32(k_smem + slot * LT::kTileBytes);
+                // Descriptors differ from the precomputed bases only in the 16-byte address field.
+                const uint64_t q_desc = q_desc0 + uint64_t((qb * LT::kQBytes) >> 4);
+                const uint64_t k_desc = k_desc0 + uint64_t((slot * LT::kTileBytes) >> 4);
                 const uint32_t s_tmem = tmem + ((t & 1) ? LT::kSCol1 : LT::kSCol0);
                 #pragma unroll
                 for (int b = 0; b < LT::kBlocks; ++b) {
                     #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
-                        const uint32_t off = b * (kRows * 128) + ks * 32;
-                        mma_ss(s_tmem, smem_desc(q_addr + off, 16), smem_desc(k_addr + off, 16), idesc_qk,
-                               (b | ks) != 0 ? 1u : 0u);
+                        const uint64_t off = uint64_t((b * (kRows * 128) + ks * 32) >> 4);
+                        mma_ss(s_tmem, q_desc + off, k_desc + off, idesc_qk, (b | ks) != 0 ? 1u : 0u);
                     }
                 }
                 tc_commit(&bars->k_empty[slot]);
@@ -251,20 +256,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     if (t >= LT::kOBufs &&
                         !mbar_wait(&bars->o_free[ob], (t / LT::kOBufs - 1) & 1, abort_flag, args.status, 7)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t v_addr = smem_u32(v_smem + slot * LT::kTileBytes);
+                    const uint32_t v_addr = v_base + slot * LT::kTileBytes;
                     const uint32_t p_tmem = tmem + ((t & 1) ? LT::kSCol1 : LT::kSCol0);
                     const uint32_t o_tmem = tmem + LT::kOCol0 + ob * LT::kOStride;
+                    const uint32_t block_stride = LT::kSumOnTensor ? ones_addr - v_addr : uint32_t(kTileKeys * 128);
+                    const uint64_t v_desc = smem_desc(v_addr, block_stride);
                     #pragma unroll
                     for (int ks = 0; ks < kTileKeys / 16; ++ks) {
-                        mma_ts(o_tmem, p_tmem + ks * 8, smem_desc(v_addr + ks * 2048, kTileKeys * 128), idesc_pv,
-                               ks != 0 ? 1u : 0u);
-                    }
-                    if (LT::kSumOnTensor) {
-                        // Row sums of P on the tensor core: P x ones, 16 identical columns beside O.
-                        #pragma unroll
-                        for (int ks = 0; ks < kTileKeys / 16; ++ks) {
-                            mma_ts(o_tmem + D, p_tmem + ks * 8, ones_desc, idesc_sum, ks != 0 ? 1u : 0u);
-                        }
+                        mma_ts(o_tmem, p_tmem + ks * 8, v_desc + uint64_t((ks * 2048) >> 4), idesc_pv, ks != 0 ? 1u : 0u);
                     }
                     tc_commit(&bars->v_empty[slot]);
                     tc_commit(&bars->o_full[ob]);
@@ -312,80 +311,84 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 const int key0 = (w.tile_first + j * world) * kTileKeys + half * 64;
                 if (args.decode && LT::kSumOnTensor) {
                     // Decode has at most 16 real rows, all in quadrant 0 and all at one position.  The
-                    // 16x256b shape spreads each row over four threads, so the warp computes 16 x 64
-                    // weights instead of 32 x 64.  Element for element the weights are the ones the
-                    // prefill layout computes; the row sums come from the tensor core either way.
+                    // 16x256b shape spreads each row over four threads, so a warp computes 16 x 128
+                    // weights instead of 32 x 128.  The two softmax groups take alternate tiles (one
+                    // warp each), so two tiles are in flight.  Element for element the weights are the
+                    // ones the prefill layout computes; the row sums come from the tensor core either way.
+                    if (int(t & 1) != half) {
+                        tc_fence_before();
+                        mbar_arrive(&bars->p_full[sb]);
+                        continue;
+                    }
                     const int q4 = lane & 3;
-                    const int c_lo = max(0, w.first_pos - (args.window > 0 ? args.window - 1 : w.first_pos)) - key0;
-                    const int c_hi = w.first_pos - key0;
+                    const int tile_key0 = (w.tile_first + j * world) * kTileKeys;
+                    const int c_lo = (args.window > 0 ? max(0, w.first_pos - args.window + 1) : 0) - tile_key0;
+                    const int c_hi = w.first_pos - tile_key0;
                     const bool upper = G > 8;                // rows 8-15 hold heads only when the group is 16
-                    uint32_t v[32];
-                    HC_TMEM_LD_16x256b_x8(s_tmem + half * 64, v);
+                    uint32_t v[2][32];
+                    HC_TMEM_LD_16x256b_x8(s_tmem, v[0]);
+                    HC_TMEM_LD_16x256b_x8(s_tmem + 64, v[1]);
                     tc_wait_ld();
                     TC_LAP(1)
-                    if (!(c_lo <= 0 && c_hi >= 63)) {
+                    if (!(c_lo <= 0 && c_hi >= kTileKeys - 1)) {
                         #pragma unroll
-                        for (int n = 0; n < 8; ++n) {
+                        for (int hb = 0; hb < 2; ++hb) {
                             #pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-                                const int col = 8 * n + 2 * q4 + e;
-                                if (col < c_lo || col > c_hi) {
-                                    v[4 * n + e] = __float_as_uint(neg_inf);
-                                    v[4 * n + 2 + e] = __float_as_uint(neg_inf);
+                            for (int n = 0; n < 8; ++n) {
+                                #pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const int col = 64 * hb + 8 * n + 2 * q4 + e;
+                                    if (col < c_lo || col > c_hi) {
+                                        v[hb][4 * n + e] = __float_as_uint(neg_inf);
+                                        v[hb][4 * n + 2 + e] = __float_as_uint(neg_inf);
+                                    }
                                 }
                             }
                         }
                     }
-                    // Row maxima: this thread's 16 columns, then the four threads of the row, then the
-                    // other half of the tile through shared memory.
-                    float mrow[2] = {neg_inf, neg_inf};
+                    // Row maxima: this thread's 32 columns, then the four threads of the row.
+                    float neg_mc[2] = {0.0f, 0.0f};
                     #pragma unroll
                     for (int rs = 0; rs < 2; ++rs) {
                         if (rs == 0 || upper) {
-                            float m0 = __uint_as_float(v[2 * rs]), m1 = __uint_as_float(v[2 * rs + 1]);
+                            float m0 = __uint_as_float(v[0][2 * rs]), m1 = __uint_as_float(v[0][2 * rs + 1]);
+                            float m2 = __uint_as_float(v[1][2 * rs]), m3 = __uint_as_float(v[1][2 * rs + 1]);
                             #pragma unroll
-                            for (int n = 1; n < 8; n += 2) {
-                                if (n + 1 < 8) {
-                                    m0 = fmax3(m0, __uint_as_float(v[4 * n + 2 * rs]), __uint_as_float(v[4 * (n + 1) + 2 * rs]));
-                                    m1 = fmax3(m1, __uint_as_float(v[4 * n + 2 * rs + 1]), __uint_as_float(v[4 * (n + 1) + 2 * rs + 1]));
-                                } else {
-                                    m0 = fmaxf(m0, __uint_as_float(v[4 * n + 2 * rs]));
-                                    m1 = fmaxf(m1, __uint_as_float(v[4 * n + 2 * rs + 1]));
-                                }
+                            for (int n = 1; n < 7; n += 2) {
+                                m0 = fmax3(m0, __uint_as_float(v[0][4 * n + 2 * rs]), __uint_as_float(v[0][4 * (n + 1) + 2 * rs]));
+                                m1 = fmax3(m1, __uint_as_float(v[0][4 * n + 2 * rs + 1]), __uint_as_float(v[0][4 * (n + 1) + 2 * rs + 1]));
+                                m2 = fmax3(m2, __uint_as_float(v[1][4 * n + 2 * rs]), __uint_as_float(v[1][4 * (n + 1) + 2 * rs]));
+                                m3 = fmax3(m3, __uint_as_float(v[1][4 * n + 2 * rs + 1]), __uint_as_float(v[1][4 * (n + 1) + 2 * rs + 1]));
                             }
-                            float m = fmaxf(m0, m1);
+                            m0 = fmax3(m0, __uint_as_float(v[0][28 + 2 * rs]), m1);
+                            m2 = fmax3(m2, __uint_as_float(v[1][28 + 2 * rs]), m3);
+                            float m = fmax3(fmaxf(m0, m2), __uint_as_float(v[0][29 + 2 * rs]), __uint_as_float(v[1][29 + 2 * rs]));
                             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
                             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-                            mrow[rs] = m;
-                            if (q4 == 0) bars->xmax[sb][half][(lane >> 2) + 8 * rs] = m;
+                            neg_mc[rs] = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
+                            if (q4 == 0) bars->mm[t & 3][(lane >> 2) + 8 * rs] = __fmul_rn(m, args.c);
                         }
                     }
                     TC_LAP(2)
-                    mbar_arrive(&bars->x_bar[quad]);
-                    if (!mbar_wait(&bars->x_bar[quad], xuse & 1, abort_flag, args.status, 11)) { ok = false; break; }
-                    ++xuse;
-                    TC_LAP(4)
                     // st[2n + rs]: P column 4n + q4 of row lane/4 + 8 rs, the layout of the 16x128b store.
-                    uint32_t st[16];
                     #pragma unroll
-                    for (int rs = 0; rs < 2; ++rs) {
-                        if (rs == 0 || upper) {
-                            const int r = (lane >> 2) + 8 * rs;
-                            const float m = fmaxf(mrow[rs], bars->xmax[sb][half ^ 1][r]);
-                            const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
-                            if (half == 0 && q4 == 0) bars->mm[t & 3][r] = __fmul_rn(m, args.c);
+                    for (int hb = 0; hb < 2; ++hb) {
+                        uint32_t st[16];
+                        #pragma unroll
+                        for (int rs = 0; rs < 2; ++rs) {
                             #pragma unroll
                             for (int n = 0; n < 8; ++n) {
-                                const float e0 = tile_weight_raw(__uint_as_float(v[4 * n + 2 * rs]), neg_mc, args.c);
-                                const float e1 = tile_weight_raw(__uint_as_float(v[4 * n + 2 * rs + 1]), neg_mc, args.c);
-                                st[2 * n + rs] = pack_bf16x2(e0, e1);
+                                if (rs == 0 || upper) {
+                                    const float e0 = tile_weight_raw(__uint_as_float(v[hb][4 * n + 2 * rs]), neg_mc[rs], args.c);
+                                    const float e1 = tile_weight_raw(__uint_as_float(v[hb][4 * n + 2 * rs + 1]), neg_mc[rs], args.c);
+                                    st[2 * n + rs] = pack_bf16x2(e0, e1);
+                                } else {
+                                    st[2 * n + rs] = 0u;
+                                }
                             }
-                        } else {
-                            #pragma unroll
-                            for (int n = 0; n < 8; ++n) st[2 * n + rs] = 0u;
                         }
+                        HC_TMEM_ST_16x128b_x8(s_tmem + hb * 32, st);
                     }
-                    HC_TMEM_ST_16x128b_x8(s_tmem + half * 32, st);
                     tc_wait_st();
                     tc_fence_before();
                     mbar_arrive(&bars->p_full[sb]);
@@ -808,8 +811,7 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
     args.ep = ep;
     args.status = ctx->status_dev;
     args.decode = 1;
-    // Items of consecutive tiles, about eight per CTA so that the static round-robin balances.  The
-    // head_dim 256 kernel does not look ahead across items, so it gets about one item per CTA.
+    // Items of consecutive tiles, about eight per CTA so that the static round-robin balances.  The head_dim 256 kernel does not look ahead across items: about one item per CTA.
     const long long target = (shape.head_dim == 256 ? 1LL : 8LL) * std::max(ctx->sm_count, 1);
     long long per = (total_tiles * shape.kv_heads + target - 1) / target;
     args.tiles_per_item = int(std::min<long long>(std::max<long long>(per, 1), 64));
