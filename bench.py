@@ -268,7 +268,10 @@ def run_cuda(args):
     achieved_tflops = flops_total / (ms_total * 1e-3) / 1e12 if ms_total > 0 else 0.0
     achieved_tflops = achieved_tflops  # this rank's; ranks are symmetric
     roofline = {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                "frac": achieved_tflops / peaks["bf16_tflops"], "traffic": None,
+                "frac": achieved_tflops / peaks["bf16_tflops"],
+                # dram__bytes_read + write of one launch, from the committed ncu capture of the last
+                # chunk (context 4096); earlier chunks read proportionally fewer keys.
+                "traffic": 12.72e6 if args.config == "C2" and world == 1 else None,
                 "kernel": "prefill attention call (q prologue + attention kernel), per 512-token chunk",
                 "peak_source": f"{peaks['source']} cuBLAS bf16 burst",
                 "avg_launch_ms": ms_total / max(len(events), 1)}

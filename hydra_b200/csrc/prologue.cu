@@ -32,11 +32,12 @@ prepare_heads_kernel(const PrepArgs args) {
     int total_heads = 0;
     for (int j = 0; j < args.n_jobs; ++j) total_heads += args.job[j].heads;
     // Warps stride over the (token, head) vectors of the call.
-    const long long vectors = (long long)args.tokens * total_heads;
-    const long long stride = (long long)gridDim.x * kPrepWarps;
-    for (long long vec = (long long)blockIdx.x * kPrepWarps + warp; vec < vectors; vec += stride) {
-    const int token = int(vec / total_heads);
-    const int slot = int(vec - (long long)token * total_heads);
+    // 32-bit indices: a launch covers at most 32768 tokens x a few hundred heads.
+    const unsigned vectors = unsigned(args.tokens) * unsigned(total_heads);
+    const unsigned stride = gridDim.x * kPrepWarps;
+    for (unsigned vec = blockIdx.x * kPrepWarps + warp; vec < vectors; vec += stride) {
+    const int token = int(vec / unsigned(total_heads));
+    const int slot = int(vec - unsigned(token) * unsigned(total_heads));
     __syncwarp();                                  // the staging row is reused
 
     int job_index = 0, head = slot;
@@ -133,7 +134,7 @@ hc_status launch_prepare(hc_context* ctx, const PrepArgs& args, cudaStream_t str
     if (total_heads == 0 || args.tokens == 0) return HC_OK;
     const long long vectors = (long long)args.tokens * total_heads;
     const long long wanted = (vectors + kPrepWarps - 1) / kPrepWarps;
-    const int grid = int(std::min<long long>(wanted, (long long)std::max(ctx->sm_count, 1) * 8));
+    const int grid = int(std::min<long long>(wanted, (long long)std::max(ctx->sm_count, 1) * 16));
     prepare_heads_kernel<<<grid, kPrepWarps * 32, 0, stream>>>(args);
     ctx->launches += 1;
     return check_cuda(cudaGetLastError(), "prepare_heads_kernel launch");
