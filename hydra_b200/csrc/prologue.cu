@@ -21,6 +21,61 @@ namespace {
 constexpr int kPrepWarps = 8;
 constexpr int kMaxHeadDim = 512;
 
+// One head vector of 32 * PER elements handled by one warp with no staging: lane l holds elements
+// l + 32 j, so both members of every rotation pair (i, i + d/2) sit in one lane.  The arithmetic and
+// its order are those of the staged path below.
+template <int PER>
+__device__ __forceinline__ void prepare_in_lanes(const PrepJob& job, size_t src_base, uint16_t* dst16,
+                                                 const float* cos_row, const float* sin_row, float eps, int lane) {
+    constexpr int kHalfPer = PER / 2;
+    constexpr int d = 32 * PER;
+    constexpr int half = d / 2;
+    float xv[PER], cv[kHalfPer], sv[kHalfPer];
+    #pragma unroll
+    for (int j = 0; j < PER; ++j) xv[j] = load_io(job.src, src_base + lane + 32 * j, job.src_dtype);
+    if (cos_row) {
+        #pragma unroll
+        for (int j = 0; j < kHalfPer; ++j) {
+            cv[j] = cos_row[lane + 32 * j];
+            sv[j] = sin_row[lane + 32 * j];
+        }
+    }
+    if (job.norm != 0) {
+        float sum = 0.0f;
+        #pragma unroll
+        for (int j = 0; j < PER; ++j) sum = __fmaf_rn(xv[j], xv[j], sum);
+        #pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, offset));
+        }
+        const float inverse = __frsqrt_rn(__fadd_rn(__fdiv_rn(sum, float(d)), eps));
+        #pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            float value = __fmul_rn(xv[j], inverse);
+            if (job.norm == 1) value = __fmul_rn(value, bf16_bits_to_float(job.weight[lane + 32 * j]));
+            xv[j] = value;
+        }
+    }
+    #pragma unroll
+    for (int j = 0; j < kHalfPer; ++j) {
+        float x1 = xv[j], x2 = xv[j + kHalfPer];
+        if (cos_row) {
+            const float r1 = __fmaf_rn(x1, cv[j], -__fmul_rn(x2, sv[j]));
+            const float r2 = __fmaf_rn(x2, cv[j], __fmul_rn(x1, sv[j]));
+            x1 = r1;
+            x2 = r2;
+        }
+        const int i = lane + 32 * j;
+        if (job.kind == 3) {
+            store_io(job.dst, src_base + i, job.src_dtype, x1);
+            store_io(job.dst, src_base + half + i, job.src_dtype, x2);
+        } else {
+            dst16[i] = float_to_bf16_bits(x1);
+            dst16[half + i] = float_to_bf16_bits(x2);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kPrepWarps * 32)
 prepare_heads_kernel(const PrepArgs args) {
     __shared__ float stage[kPrepWarps][kMaxHeadDim];
@@ -38,8 +93,6 @@ prepare_heads_kernel(const PrepArgs args) {
     for (unsigned vec = blockIdx.x * kPrepWarps + warp; vec < vectors; vec += stride) {
     const int token = int(vec / unsigned(total_heads));
     const int slot = int(vec - unsigned(token) * unsigned(total_heads));
-    __syncwarp();                                  // the staging row is reused
-
     int job_index = 0, head = slot;
     while (head >= args.job[job_index].heads) {
         head -= args.job[job_index].heads;
@@ -53,8 +106,35 @@ prepare_heads_kernel(const PrepArgs args) {
         if (!row_is_local(args.cache.map, position)) continue;   // another rank owns this key tile
     }
 
-    float* x = stage[warp];
     const size_t src_base = size_t(token) * size_t(job.token_stride) + size_t(head) * job.head_stride;
+    const bool rotate = job.rope != 0;
+    const int table_row = position < args.table_positions ? position : args.table_positions - 1;
+    // Destination of this head vector.
+    uint16_t* dst16 = nullptr;
+    if (job.kind == 0) {
+        dst16 = reinterpret_cast<uint16_t*>(job.dst) + (size_t(token) * job.heads + head) * d;
+    } else if (job.kind == 1 || job.kind == 2) {
+        const int row = row_of_position(args.cache.map, position);
+        uint16_t* base = job.kind == 1 ? args.cache.k : args.cache.v;
+        dst16 = base + ((size_t(seq) * args.cache.kv_heads + head) * args.cache.capacity + row) * d;
+    }
+
+    if ((half & 31) == 0) {
+        // Fast path (head_dim 64, 128, 256, 512): no staging, all loads issued up front.
+        const float* cos_row = rotate ? args.cos + size_t(table_row) * half : nullptr;
+        const float* sin_row = rotate ? args.sin + size_t(table_row) * half : nullptr;
+        switch (d >> 5) {
+            case 2: prepare_in_lanes<2>(job, src_base, dst16, cos_row, sin_row, args.eps, lane); break;
+            case 4: prepare_in_lanes<4>(job, src_base, dst16, cos_row, sin_row, args.eps, lane); break;
+            case 8: prepare_in_lanes<8>(job, src_base, dst16, cos_row, sin_row, args.eps, lane); break;
+            default: prepare_in_lanes<16>(job, src_base, dst16, cos_row, sin_row, args.eps, lane); break;
+        }
+        continue;
+    }
+
+    // General path (small or odd head dims): stage the vector in shared memory.
+    __syncwarp();                                  // the staging row is reused
+    float* x = stage[warp];
     float sum = 0.0f;
     for (int i = lane; i < d; i += 32) {
         const float value = load_io(job.src, src_base + i, job.src_dtype);
@@ -74,19 +154,6 @@ prepare_heads_kernel(const PrepArgs args) {
         }
     }
     __syncwarp();
-
-    // Destination of this head vector.
-    uint16_t* dst16 = nullptr;
-    if (job.kind == 0) {
-        dst16 = reinterpret_cast<uint16_t*>(job.dst) + (size_t(token) * job.heads + head) * d;
-    } else if (job.kind == 1 || job.kind == 2) {
-        const int row = row_of_position(args.cache.map, position);
-        uint16_t* base = job.kind == 1 ? args.cache.k : args.cache.v;
-        dst16 = base + ((size_t(seq) * args.cache.kv_heads + head) * args.cache.capacity + row) * d;
-    }
-
-    const bool rotate = job.rope != 0;
-    const int table_row = position < args.table_positions ? position : args.table_positions - 1;
     for (int i = lane; i < half; i += 32) {
         float x1 = x[i], x2 = x[half + i];
         if (rotate) {
