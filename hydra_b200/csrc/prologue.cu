@@ -9,7 +9,8 @@
 // (Sources/HydraReference/Gemma4ReferenceLayer.swift:154-157, 234-246); v is normalised without a
 // weight and never rotated.
 //
-// One warp handles one head vector.  HBM-bound and tiny: a chunk of 512 tokens moves a few MB.
+// HBM-bound and tiny: a chunk of 512 tokens moves a few MB, so what matters is how many bytes each
+// warp has in flight.
 
 #include <algorithm>
 
@@ -21,61 +22,139 @@ namespace {
 constexpr int kPrepWarps = 8;
 constexpr int kMaxHeadDim = 512;
 
-// One head vector of 32 * PER elements handled by one warp with no staging: lane l holds elements
-// l + 32 j, so both members of every rotation pair (i, i + d/2) sit in one lane.  The arithmetic and
-// its order are those of the staged path below.
-template <int PER>
-__device__ __forceinline__ void prepare_in_lanes(const PrepJob& job, size_t src_base, uint16_t* dst16,
-                                                 const float* cos_row, const float* sin_row, float eps, int lane) {
-    constexpr int kHalfPer = PER / 2;
-    constexpr int d = 32 * PER;
-    constexpr int half = d / 2;
-    float xv[PER], cv[kHalfPer], sv[kHalfPer];
-    #pragma unroll
-    for (int j = 0; j < PER; ++j) xv[j] = load_io(job.src, src_base + lane + 32 * j, job.src_dtype);
-    if (cos_row) {
-        #pragma unroll
-        for (int j = 0; j < kHalfPer; ++j) {
-            cv[j] = cos_row[lane + 32 * j];
-            sv[j] = sin_row[lane + 32 * j];
-        }
+// Four consecutive elements of an activation row as fp32 (8-byte load for bf16, 16-byte for fp32).
+__device__ __forceinline__ void load_io4(const void* base, size_t index, int dtype, float (&out)[4]) {
+    if (dtype == 0) {
+        const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + index);
+        out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    } else {
+        const uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + index);
+        out[0] = bf16_bits_to_float(uint16_t(v.x & 0xffffu));
+        out[1] = bf16_bits_to_float(uint16_t(v.x >> 16));
+        out[2] = bf16_bits_to_float(uint16_t(v.y & 0xffffu));
+        out[3] = bf16_bits_to_float(uint16_t(v.y >> 16));
     }
-    if (job.norm != 0) {
-        float sum = 0.0f;
-        #pragma unroll
-        for (int j = 0; j < PER; ++j) sum = __fmaf_rn(xv[j], xv[j], sum);
-        #pragma unroll
-        for (int offset = 16; offset > 0; offset >>= 1) {
-            sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, offset));
-        }
-        const float inverse = __frsqrt_rn(__fadd_rn(__fdiv_rn(sum, float(d)), eps));
-        #pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            float value = __fmul_rn(xv[j], inverse);
-            if (job.norm == 1) value = __fmul_rn(value, bf16_bits_to_float(job.weight[lane + 32 * j]));
-            xv[j] = value;
-        }
+}
+__device__ __forceinline__ uint2 pack_bf16x4(const float (&v)[4]) {
+    uint2 r;
+    r.x = uint32_t(float_to_bf16_bits(v[0])) | (uint32_t(float_to_bf16_bits(v[1])) << 16);
+    r.y = uint32_t(float_to_bf16_bits(v[2])) | (uint32_t(float_to_bf16_bits(v[3])) << 16);
+    return r;
+}
+__device__ __forceinline__ void store_io4(void* base, size_t index, int dtype, const float (&v)[4]) {
+    if (dtype == 0) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + index) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(base) + index) = pack_bf16x4(v);
     }
-    #pragma unroll
-    for (int j = 0; j < kHalfPer; ++j) {
-        float x1 = xv[j], x2 = xv[j + kHalfPer];
-        if (cos_row) {
-            const float r1 = __fmaf_rn(x1, cv[j], -__fmul_rn(x2, sv[j]));
-            const float r2 = __fmaf_rn(x2, cv[j], __fmul_rn(x1, sv[j]));
-            x1 = r1;
-            x2 = r2;
+}
+
+// The kernel for head_dim 64, 128 and 256 (LPV = head_dim / 8 lanes per head vector, so a warp holds
+// 4, 2 or 1 vectors at a time).  Lane m of a vector owns elements 4m..4m+3 of each half, which keeps
+// both members of every rotation pair (i, i + d/2) in one lane and makes every access an 8- or 16-byte
+// one.  The launcher checks the alignment this needs and otherwise uses the general kernel below.
+template <int LPV>
+__global__ void __launch_bounds__(kPrepWarps * 32)
+prepare_heads_vec_kernel(const PrepArgs args, int total_heads) {
+    constexpr int d = 8 * LPV;
+    constexpr int half = 4 * LPV;
+    constexpr int kPerWarp = 32 / LPV;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int sub = lane / LPV;
+    const int m = lane % LPV;
+    // 32-bit indices: a launch covers at most 32768 tokens x a few hundred heads.
+    const unsigned vectors = unsigned(args.tokens) * unsigned(total_heads);
+    const unsigned groups = (vectors + kPerWarp - 1) / kPerWarp;
+    const unsigned stride = gridDim.x * kPrepWarps;
+    for (unsigned grp = blockIdx.x * kPrepWarps + warp; grp < groups; grp += stride) {
+        unsigned vec = grp * kPerWarp + sub;
+        bool active = vec < vectors;
+        if (!active) vec = vectors - 1;              // keeps the lane's loads legal; nothing is stored
+        const int token = int(vec / unsigned(total_heads));
+        int head = int(vec - unsigned(token) * unsigned(total_heads));
+        int job_index = 0;
+        while (head >= args.job[job_index].heads) {
+            head -= args.job[job_index].heads;
+            ++job_index;
         }
-        const int i = lane + 32 * j;
-        if (job.kind == 3) {
-            store_io(job.dst, src_base + i, job.src_dtype, x1);
-            store_io(job.dst, src_base + half + i, job.src_dtype, x2);
+        const PrepJob& job = args.job[job_index];
+        const int position = args.batched ? args.meta.pos[token] : args.first_position + token;
+        const int seq = args.batched ? args.meta.seq[token] : args.seq;
+        const bool to_cache = job.kind == 1 || job.kind == 2;
+        if (to_cache && !row_is_local(args.cache.map, position)) active = false;   // another rank's tile
+
+        const size_t src_base = size_t(token) * size_t(job.token_stride) + size_t(head) * job.head_stride;
+        float x[8];
+        {
+            float lo[4], hi[4];
+            load_io4(job.src, src_base + 4 * m, job.src_dtype, lo);
+            load_io4(job.src, src_base + half + 4 * m, job.src_dtype, hi);
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) { x[j] = lo[j]; x[4 + j] = hi[j]; }
+        }
+        float4 cosv = make_float4(1.0f, 1.0f, 1.0f, 1.0f), sinv = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (job.rope != 0) {
+            const int table_row = position < args.table_positions ? position : args.table_positions - 1;
+            cosv = *reinterpret_cast<const float4*>(args.cos + size_t(table_row) * half + 4 * m);
+            sinv = *reinterpret_cast<const float4*>(args.sin + size_t(table_row) * half + 4 * m);
+        }
+        if (job.norm != 0) {
+            float sum = 0.0f;
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) sum = __fmaf_rn(x[j], x[j], sum);
+            #pragma unroll
+            for (int offset = LPV / 2; offset > 0; offset >>= 1) {
+                sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, offset));
+            }
+            const float inverse = __frsqrt_rn(__fadd_rn(__fdiv_rn(sum, float(d)), args.eps));
+            #pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], inverse);
+            if (job.norm == 1) {
+                float wl[4], wh[4];
+                load_io4(job.weight, size_t(4 * m), 1, wl);
+                load_io4(job.weight, size_t(half + 4 * m), 1, wh);
+                #pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    x[j] = __fmul_rn(x[j], wl[j]);
+                    x[4 + j] = __fmul_rn(x[4 + j], wh[j]);
+                }
+            }
+        }
+        float lo[4], hi[4];
+        if (job.rope != 0) {
+            const float c[4] = {cosv.x, cosv.y, cosv.z, cosv.w};
+            const float s[4] = {sinv.x, sinv.y, sinv.z, sinv.w};
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                lo[j] = __fmaf_rn(x[j], c[j], -__fmul_rn(x[4 + j], s[j]));
+                hi[j] = __fmaf_rn(x[4 + j], c[j], __fmul_rn(x[j], s[j]));
+            }
         } else {
-            dst16[i] = float_to_bf16_bits(x1);
-            dst16[half + i] = float_to_bf16_bits(x2);
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) { lo[j] = x[j]; hi[j] = x[4 + j]; }
+        }
+        if (!active) continue;
+        if (job.kind == 3) {
+            store_io4(job.dst, src_base + 4 * m, job.src_dtype, lo);
+            store_io4(job.dst, src_base + half + 4 * m, job.src_dtype, hi);
+        } else {
+            uint16_t* dst16;
+            if (job.kind == 0) {
+                dst16 = reinterpret_cast<uint16_t*>(job.dst) + (size_t(token) * job.heads + head) * d;
+            } else {
+                const int row = row_of_position(args.cache.map, position);
+                uint16_t* base = job.kind == 1 ? args.cache.k : args.cache.v;
+                dst16 = base + ((size_t(seq) * args.cache.kv_heads + head) * args.cache.capacity + row) * d;
+            }
+            *reinterpret_cast<uint2*>(dst16 + 4 * m) = pack_bf16x4(lo);
+            *reinterpret_cast<uint2*>(dst16 + half + 4 * m) = pack_bf16x4(hi);
         }
     }
 }
 
+// The general kernel: any even head_dim up to 512, any alignment.  One warp per head vector, staged
+// in shared memory.
 __global__ void __launch_bounds__(kPrepWarps * 32)
 prepare_heads_kernel(const PrepArgs args) {
     __shared__ float stage[kPrepWarps][kMaxHeadDim];
@@ -119,20 +198,7 @@ prepare_heads_kernel(const PrepArgs args) {
         dst16 = base + ((size_t(seq) * args.cache.kv_heads + head) * args.cache.capacity + row) * d;
     }
 
-    if ((half & 31) == 0) {
-        // Fast path (head_dim 64, 128, 256, 512): no staging, all loads issued up front.
-        const float* cos_row = rotate ? args.cos + size_t(table_row) * half : nullptr;
-        const float* sin_row = rotate ? args.sin + size_t(table_row) * half : nullptr;
-        switch (d >> 5) {
-            case 2: prepare_in_lanes<2>(job, src_base, dst16, cos_row, sin_row, args.eps, lane); break;
-            case 4: prepare_in_lanes<4>(job, src_base, dst16, cos_row, sin_row, args.eps, lane); break;
-            case 8: prepare_in_lanes<8>(job, src_base, dst16, cos_row, sin_row, args.eps, lane); break;
-            default: prepare_in_lanes<16>(job, src_base, dst16, cos_row, sin_row, args.eps, lane); break;
-        }
-        continue;
-    }
-
-    // General path (small or odd head dims): stage the vector in shared memory.
+    // Stage the vector in shared memory.
     __syncwarp();                                  // the staging row is reused
     float* x = stage[warp];
     float sum = 0.0f;
@@ -195,14 +261,36 @@ __global__ void output_gate_kernel(void* output, const void* gate, size_t count,
 
 }  // namespace
 
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 hc_status launch_prepare(hc_context* ctx, const PrepArgs& args, cudaStream_t stream) {
     int total_heads = 0;
     for (int j = 0; j < args.n_jobs; ++j) total_heads += args.job[j].heads;
     if (total_heads == 0 || args.tokens == 0) return HC_OK;
     const long long vectors = (long long)args.tokens * total_heads;
-    const long long wanted = (vectors + kPrepWarps - 1) / kPrepWarps;
-    const int grid = int(std::min<long long>(wanted, (long long)std::max(ctx->sm_count, 1) * 16));
-    prepare_heads_kernel<<<grid, kPrepWarps * 32, 0, stream>>>(args);
+    const int d = args.head_dim;
+    const long long cap = (long long)std::max(ctx->sm_count, 1) * 16;
+    // The vector kernel needs 16-byte aligned rows everywhere it touches.
+    bool vector_ok = d == 64 || d == 128 || d == 256;
+    for (int j = 0; j < args.n_jobs && vector_ok; ++j) {
+        const PrepJob& job = args.job[j];
+        if (job.heads == 0) continue;
+        vector_ok = aligned16(job.src) && job.token_stride % 8 == 0 && job.head_stride % 8 == 0 &&
+                    (job.norm != 1 || aligned16(job.weight)) &&
+                    ((job.kind != 0 && job.kind != 3) || aligned16(job.dst));
+    }
+    if (vector_ok) {
+        const int per_warp = 256 / d;
+        const long long groups = (vectors + per_warp - 1) / per_warp;
+        const int grid = int(std::min<long long>((groups + kPrepWarps - 1) / kPrepWarps, cap));
+        if (d == 64) prepare_heads_vec_kernel<8><<<grid, kPrepWarps * 32, 0, stream>>>(args, total_heads);
+        else if (d == 128) prepare_heads_vec_kernel<16><<<grid, kPrepWarps * 32, 0, stream>>>(args, total_heads);
+        else prepare_heads_vec_kernel<32><<<grid, kPrepWarps * 32, 0, stream>>>(args, total_heads);
+    } else {
+        const long long wanted = (vectors + kPrepWarps - 1) / kPrepWarps;
+        const int grid = int(std::min<long long>(wanted, cap));
+        prepare_heads_kernel<<<grid, kPrepWarps * 32, 0, stream>>>(args);
+    }
     ctx->launches += 1;
     return check_cuda(cudaGetLastError(), "prepare_heads_kernel launch");
 }
