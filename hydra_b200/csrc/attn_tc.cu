@@ -190,8 +190,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             }
         }
     } else if (warp == 1) {
-        // ===== MMA issuer: S(t + 1) is issued before P(t) is awaited, across item boundaries too =====
-        if (lane == 0) {
+        // ===== MMA issuer: S(t + 1) is issued before P(t) is awaited, across item boundaries too.
+        // The whole warp walks the loop and waits, so control flow stays warp-uniform; one elected
+        // lane issues the tcgen05 instructions. =====
+        {
             constexpr uint32_t idesc_qk = instr_desc(kTileKeys, false);
             // With the row sums on the tensor core, P V and P x ones are one instruction: the B operand
             // is the V tile (64 columns) followed by a block of ones that the descriptor's
@@ -201,15 +203,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const uint32_t v_base = smem_u32(v_smem);
             const uint64_t q_desc0 = smem_desc(smem_u32(q_smem), 16);
             const uint64_t k_desc0 = smem_desc(smem_u32(k_smem), 16);
+            TC_LAP_DECL
             // S = Q K^T of stream tile t; `it` is the ordinal of its item, `last` marks its item's last tile.
             auto issue_qk = [&](uint32_t t, uint32_t it, bool first, bool last) -> bool {
                 const int slot = int(t % LT::kStages);
                 const int qb = int(it & 1);
                 if (first && !mbar_wait(&bars->q_full[qb], (it >> 1) & 1, abort_flag, args.status, 4)) return false;
-                TC_TRACE(3);
                 if (!mbar_wait(&bars->k_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 3)) return false;
-                TC_TRACE(4);
                 tc_fence_after();
+                TC_LAP(0)
+                if (elect_one()) {
                 // Descriptors differ from the precomputed bases only in the 16-byte address field.
                 const uint64_t q_desc = q_desc0 + uint64_t((qb * LT::kQBytes) >> 4);
                 const uint64_t k_desc = k_desc0 + uint64_t((slot * LT::kTileBytes) >> 4);
@@ -222,9 +225,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         mma_ss(s_tmem, q_desc + off, k_desc + off, idesc_qk, (b | ks) != 0 ? 1u : 0u);
                     }
                 }
+                TC_LAP(1)
                 tc_commit(&bars->k_empty[slot]);
                 tc_commit(&bars->s_full[t & 1]);
                 if (last) tc_commit(&bars->q_empty[qb]);        // the item's Q tile has been read for the last time
+                TC_LAP(2)
+                }
+                __syncwarp();
                 return true;
             };
             uint32_t t = 0, it = 0;
@@ -256,6 +263,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     if (t >= LT::kOBufs &&
                         !mbar_wait(&bars->o_free[ob], (t / LT::kOBufs - 1) & 1, abort_flag, args.status, 7)) { ok = false; break; }
                     tc_fence_after();
+                    TC_LAP(3)
+                    if (elect_one()) {
                     const uint32_t v_addr = v_base + slot * LT::kTileBytes;
                     const uint32_t p_tmem = tmem + ((t & 1) ? LT::kSCol1 : LT::kSCol0);
                     const uint32_t o_tmem = tmem + LT::kOCol0 + ob * LT::kOStride;
@@ -265,14 +274,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     for (int ks = 0; ks < kTileKeys / 16; ++ks) {
                         mma_ts(o_tmem, p_tmem + ks * 8, v_desc + uint64_t((ks * 2048) >> 4), idesc_pv, ks != 0 ? 1u : 0u);
                     }
+                    TC_LAP(4)
                     tc_commit(&bars->v_empty[slot]);
                     tc_commit(&bars->o_full[ob]);
+                    TC_LAP(5)
+                    }
+                    __syncwarp();
                 }
                 if (!ok || nxt >= args.n_items || nxt == item) break;
                 item = nxt;
                 w = wn;
                 ++it;
             }
+            if (elect_one()) { TC_LAP_STORE(3) }
         }
     }
     } else if (wg == 1 || wg == 2) {
@@ -514,6 +528,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         uint32_t t = 0, it = 0;
         bool ok = true;
         int item = first_item(args);
+        TC_LAP_DECL
         if (item < args.n_items) stage_q(decode_item(args, item), 0);
         while (ok && item < args.n_items) {
             const TcItem w = decode_item(args, item);
@@ -544,7 +559,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             for (int i = 0; i < D; ++i) A[i] = 0.0f;
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
                 const int ob = int(t % LT::kOBufs);
+                TC_LAP(5)
                 if (!mbar_wait(&bars->o_full[ob], (t / LT::kOBufs) & 1, abort_flag, args.status, 9)) { ok = false; break; }
+                TC_LAP(0)
                 if (threadIdx.x == 384) TC_TRACE(7);
                 tc_fence_after();
                 if (!warp_has_rows) {
@@ -554,6 +571,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 }
                 const uint32_t o_tmem = tmem + lane_base + LT::kOCol0 + ob * LT::kOStride;
                 const float l_tile = tile_sum(o_tmem, t);
+                TC_LAP(1)
                 if (args.decode) {
                     // Split decode: the tile's partial goes to the workspace; merge_tiles_kernel folds.
                     const size_t prow = (size_t(w.row0) * args.q_heads + head) * args.part_tiles + (w.ordinal0 + j);
@@ -608,6 +626,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         }
                     }
                 }
+                TC_LAP(2)
             }
             if (!ok) break;
             if (valid && !args.decode) {
@@ -651,7 +670,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             if (threadIdx.x == 384) TC_TRACE(8);
             item = nxt;
             ++it;
+            TC_LAP(3)
         }
+        if (threadIdx.x == 384) { TC_LAP_STORE(2) }
         if (threadIdx.x == 384) {
 #ifdef HC_TC_TRACE
             hc_tc_trace[(blockIdx.x & 255) * 16 + 9] = 0;
