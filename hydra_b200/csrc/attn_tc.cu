@@ -66,12 +66,11 @@ struct TcBarriers {
     uint64_t q_full[2], q_empty[2];
     uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
     uint64_t s_full[2], p_full[2], o_full[2], o_free[2];
-    uint64_t x_bar[4];        // per lane quadrant: the two softmax warps that share a row exchange maxima
+    uint64_t xu_turn[2];      // the softmax warpgroups take turns in the exp2 phase
     uint32_t tmem_base;
     int abort_flag;
     float mm[4][kRows];       // per-tile scaled maxima, softmax -> fold (ring of 4 tiles)
-    float l[4][2][kRows];     // per-tile sums of each 64-column half (when not summed on the tensor core)
-    float xmax[2][2][kRows];  // per S buffer and half: that half's maximum
+    float l[4][kRows];        // per-tile row sums (when not summed on the tensor core)
 };
 
 // One unit of work of a CTA.
@@ -88,7 +87,10 @@ __device__ __forceinline__ void tc_trace(int slot) {
 #define TC_LAP_DECL long long lap_last = clock64(); long long lap_acc[6] = {0, 0, 0, 0, 0, 0};
 #define TC_LAP(k) { const long long lap_now = clock64(); lap_acc[k] += lap_now - lap_last; lap_last = lap_now; }
 #define TC_LAP_STORE(base) { for (int lap_i = 0; lap_i < 6; ++lap_i) hc_tc_trace[(blockIdx.x & 255) * 16 + 16 * 256 * (base) + lap_i] = (unsigned long long)lap_acc[lap_i]; }
+// Clock stamps of the events of stream tiles 16..23 of CTA 0 (rows 200..207 of the timeline plane).
+#define TC_EVT(t, id) { if (blockIdx.x == 0 && (t) >= 16u && (t) < 24u) hc_tc_trace[(200 + (t) - 16) * 16 + (id)] = (unsigned long long)clock64(); }
 #else
+#define TC_EVT(t, id)
 #define TC_TRACE(slot)
 #define TC_LAP_DECL
 #define TC_LAP(k)
@@ -121,12 +123,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             mbar_init(&bars->q_full[i], 128);
             mbar_init(&bars->q_empty[i], 1);
             mbar_init(&bars->s_full[i], 1);
-            mbar_init(&bars->p_full[i], 256);
+            mbar_init(&bars->p_full[i], 128);
             mbar_init(&bars->o_full[i], 1);
             mbar_init(&bars->o_free[i], 128);
+            mbar_init(&bars->xu_turn[i], 128);
         }
         for (int i = 0; i < 4; ++i) {
-            mbar_init(&bars->x_bar[i], 64);
             mbar_init(&bars->k_full[i], 1);
             mbar_init(&bars->k_empty[i], 1);
             mbar_init(&bars->v_full[i], 1);
@@ -190,9 +192,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             }
         }
     } else if (warp == 1) {
-        // ===== MMA issuer: S(t + 1) is issued before P(t) is awaited, across item boundaries too.
-        // The whole warp walks the loop and waits, so control flow stays warp-uniform; one elected
-        // lane issues the tcgen05 instructions. =====
+        // ===== MMA issuer.  Two S tiles are always in flight, one per softmax warpgroup: S(t + 2) is
+        // queued right behind P V(t), which frees the buffer they share; item boundaries do not
+        // interrupt the stream.  The whole warp walks the loop and waits, so control flow stays
+        // warp-uniform; one elected lane issues the tcgen05 instructions. =====
         {
             constexpr uint32_t idesc_qk = instr_desc(kTileKeys, false);
             // With the row sums on the tensor core, P V and P x ones are one instruction: the B operand
@@ -204,67 +207,58 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const uint64_t q_desc0 = smem_desc(smem_u32(q_smem), 16);
             const uint64_t k_desc0 = smem_desc(smem_u32(k_smem), 16);
             TC_LAP_DECL
-            // S = Q K^T of stream tile t; `it` is the ordinal of its item, `last` marks its item's last tile.
-            auto issue_qk = [&](uint32_t t, uint32_t it, bool first, bool last) -> bool {
-                const int slot = int(t % LT::kStages);
-                const int qb = int(it & 1);
-                if (first && !mbar_wait(&bars->q_full[qb], (it >> 1) & 1, abort_flag, args.status, 4)) return false;
-                if (!mbar_wait(&bars->k_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 3)) return false;
+            // S = Q K^T of the tile under the cursor.
+            auto issue_qk = [&](const TcCursor& c) -> bool {
+                const int slot = int(c.t % LT::kStages);
+                const int qb = int(c.it & 1);
+                const int sb = int(c.t & 1);
+                if (c.j == 0 && !mbar_wait(&bars->q_full[qb], (c.it >> 1) & 1, abort_flag, args.status, 4)) return false;
+                if (!mbar_wait(&bars->k_full[slot], (c.t / LT::kStages) & 1, abort_flag, args.status, 3)) return false;
                 tc_fence_after();
                 TC_LAP(0)
+                TC_EVT(c.t - 2, 3)
                 if (elect_one()) {
-                // Descriptors differ from the precomputed bases only in the 16-byte address field.
-                const uint64_t q_desc = q_desc0 + uint64_t((qb * LT::kQBytes) >> 4);
-                const uint64_t k_desc = k_desc0 + uint64_t((slot * LT::kTileBytes) >> 4);
-                const uint32_t s_tmem = tmem + ((t & 1) ? LT::kSCol1 : LT::kSCol0);
-                #pragma unroll
-                for (int b = 0; b < LT::kBlocks; ++b) {
+                    // Descriptors differ from the precomputed bases only in the 16-byte address field.
+                    const uint64_t q_desc = q_desc0 + uint64_t((qb * LT::kQBytes) >> 4);
+                    const uint64_t k_desc = k_desc0 + uint64_t((slot * LT::kTileBytes) >> 4);
+                    const uint32_t s_tmem = tmem + (sb ? LT::kSCol1 : LT::kSCol0);
                     #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t off = uint64_t((b * (kRows * 128) + ks * 32) >> 4);
-                        mma_ss(s_tmem, q_desc + off, k_desc + off, idesc_qk, (b | ks) != 0 ? 1u : 0u);
-                    }
-                }
-                TC_LAP(1)
-                tc_commit(&bars->k_empty[slot]);
-                tc_commit(&bars->s_full[t & 1]);
-                if (last) tc_commit(&bars->q_empty[qb]);        // the item's Q tile has been read for the last time
-                TC_LAP(2)
-                }
-                __syncwarp();
-                return true;
-            };
-            uint32_t t = 0, it = 0;
-            int item = first_item(args);
-            bool ok = item < args.n_items;
-            TcItem w{};
-            if (ok) {
-                w = decode_item(args, item);
-                ok = issue_qk(0, 0, true, w.n_tiles == 1);
-            }
-            while (ok) {
-                int nxt = item;
-                TcItem wn = w;
-                for (int j = 0; ok && j < w.n_tiles; ++j, ++t) {
-                    if (j + 1 < w.n_tiles) {
-                        ok = issue_qk(t + 1, it, false, j + 2 == w.n_tiles);
-                    } else {
-                        nxt = next_item(args, item);
-                        if (nxt < args.n_items) {
-                            wn = decode_item(args, nxt);
-                            ok = issue_qk(t + 1, it + 1, true, wn.n_tiles == 1);
+                    for (int b = 0; b < LT::kBlocks; ++b) {
+                        #pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            const uint64_t off = uint64_t((b * (kRows * 128) + ks * 32) >> 4);
+                            mma_ss(s_tmem, q_desc + off, k_desc + off, idesc_qk, (b | ks) != 0 ? 1u : 0u);
                         }
                     }
-                    if (!ok) break;
-                    const int slot = int(t % LT::kStages);
-                    const int ob = int(t % LT::kOBufs);
-                    if (!mbar_wait(&bars->p_full[t & 1], (t >> 1) & 1, abort_flag, args.status, 5)) { ok = false; break; }
-                    if (!mbar_wait(&bars->v_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 6)) { ok = false; break; }
-                    if (t >= LT::kOBufs &&
-                        !mbar_wait(&bars->o_free[ob], (t / LT::kOBufs - 1) & 1, abort_flag, args.status, 7)) { ok = false; break; }
-                    tc_fence_after();
-                    TC_LAP(3)
-                    if (elect_one()) {
+                    TC_LAP(1)
+                    tc_commit(&bars->k_empty[slot]);
+                    tc_commit(&bars->s_full[sb]);
+                    if (c.j + 1 == c.w.n_tiles) tc_commit(&bars->q_empty[qb]);   // the item's Q tile was read for the last time
+                    TC_LAP(2)
+                }
+                __syncwarp();
+                TC_EVT(c.t - 2, 4)
+                return true;
+            };
+            TcCursor ahead = cursor_begin(args);
+            bool ok = true;
+            for (int n = 0; ok && n < 2 && cursor_valid(args, ahead); ++n) {
+                ok = issue_qk(ahead);
+                cursor_advance(args, ahead);
+            }
+            for (TcCursor c = cursor_begin(args); ok && cursor_valid(args, c); cursor_advance(args, c)) {
+                const uint32_t t = c.t;
+                const int slot = int(t % LT::kStages);
+                const int ob = int(t % LT::kOBufs);
+                if (!mbar_wait(&bars->p_full[t & 1], (t >> 1) & 1, abort_flag, args.status, 5)) break;
+                TC_EVT(t, 0)
+                if (!mbar_wait(&bars->v_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 6)) break;
+                if (t >= LT::kOBufs &&
+                    !mbar_wait(&bars->o_free[ob], (t / LT::kOBufs - 1) & 1, abort_flag, args.status, 7)) break;
+                tc_fence_after();
+                TC_LAP(3)
+                TC_EVT(t, 1)
+                if (elect_one()) {
                     const uint32_t v_addr = v_base + slot * LT::kTileBytes;
                     const uint32_t p_tmem = tmem + ((t & 1) ? LT::kSCol1 : LT::kSCol0);
                     const uint32_t o_tmem = tmem + LT::kOCol0 + ob * LT::kOStride;
@@ -278,27 +272,32 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     tc_commit(&bars->v_empty[slot]);
                     tc_commit(&bars->o_full[ob]);
                     TC_LAP(5)
-                    }
-                    __syncwarp();
                 }
-                if (!ok || nxt >= args.n_items || nxt == item) break;
-                item = nxt;
-                w = wn;
-                ++it;
+                __syncwarp();
+                TC_EVT(t, 2)
+                if (cursor_valid(args, ahead)) {
+                    ok = issue_qk(ahead);
+                    cursor_advance(args, ahead);
+                }
             }
             if (elect_one()) { TC_LAP_STORE(3) }
         }
     }
     } else if (wg == 1 || wg == 2) {
-        // ===== softmax: two threads per row, one per 64-column half of the tile =====
+        // ===== softmax: warpgroup 1 takes the even tiles of the stream (S buffer 0), warpgroup 2 the
+        // odd ones (S buffer 1), so one group's exp2 phase overlaps the other's wait, load and
+        // maximum.  Thread = row; the row is read twice (maximum, then weights) to stay in registers. =====
         reg_dealloc<112>();
-        const int half = wg - 1;                             // 0: columns 0-63, 1: columns 64-127
+        const int parity = wg - 1;
+        const int sb = parity;
         const int quad = warp & 3;                           // the TMEM lane quadrant this warp may touch
         const int row = quad * 32 + lane;
         const int t_local = row >> args.log_group;
         const uint32_t lane_base = uint32_t(quad * 32) << 16;
+        const uint32_t s_tmem = tmem + lane_base + (sb ? LT::kSCol1 : LT::kSCol0);
         const float neg_inf = __int_as_float(0xff800000);
-        uint32_t t = 0, xuse = 0;
+        const bool take_turns = !(args.decode && LT::kSumOnTensor);
+        uint32_t t = 0;
         bool ok = true;
         TC_LAP_DECL
         for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item)) {
@@ -308,34 +307,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const int pos = valid ? w.first_pos + t_local : -1;
             const int lo = args.window > 0 ? max(0, pos - args.window + 1) : 0;
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
-                const int sb = int(t & 1);
+                if (int(t & 1) != parity) continue;
                 TC_LAP(5)
                 if (!mbar_wait(&bars->s_full[sb], (t >> 1) & 1, abort_flag, args.status, 8)) { ok = false; break; }
                 TC_LAP(0)
-                if (threadIdx.x == 128) TC_TRACE(5);
+                if ((threadIdx.x & 127) == 0) TC_EVT(t, 5)
                 tc_fence_after();
                 if (!warp_has_rows) {
                     // No query row lives in this quadrant: its P rows stay whatever they were and the
                     // O rows they produce are never read (rows are independent).
+                    if (take_turns) mbar_arrive(&bars->xu_turn[parity ^ 1]);
                     tc_fence_before();
                     mbar_arrive(&bars->p_full[sb]);
                     continue;
                 }
-                const uint32_t s_tmem = tmem + lane_base + (sb ? LT::kSCol1 : LT::kSCol0);
-                const int key0 = (w.tile_first + j * world) * kTileKeys + half * 64;
+                const int key0 = (w.tile_first + j * world) * kTileKeys;
                 if (args.decode && LT::kSumOnTensor) {
                     // Decode has at most 16 real rows, all in quadrant 0 and all at one position.  The
                     // 16x256b shape spreads each row over four threads, so a warp computes 16 x 128
-                    // weights instead of 32 x 128.  The two softmax groups take alternate tiles (one
-                    // warp each), so two tiles are in flight.  Element for element the weights are the
+                    // weights instead of 32 x 128.  Element for element the weights are the
                     // ones the prefill layout computes; the row sums come from the tensor core either way.
-                    if (int(t & 1) != half) {
-                        tc_fence_before();
-                        mbar_arrive(&bars->p_full[sb]);
-                        continue;
-                    }
                     const int q4 = lane & 3;
-                    const int tile_key0 = (w.tile_first + j * world) * kTileKeys;
+                    const int tile_key0 = key0;
                     const int c_lo = (args.window > 0 ? max(0, w.first_pos - args.window + 1) : 0) - tile_key0;
                     const int c_hi = w.first_pos - tile_key0;
                     const bool upper = G > 8;                // rows 8-15 hold heads only when the group is 16
@@ -409,85 +402,111 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     TC_LAP(3)
                     continue;
                 }
-                const int c_lo = lo - key0;                  // visible columns of this half: [c_lo, c_hi]
+                const int c_lo = lo - key0;                  // visible columns: [c_lo, c_hi]
                 const int c_hi = pos - key0;
-                uint32_t s[2][32];
-                HC_TMEM_LD32(s_tmem + half * 64, s[0]);
-                HC_TMEM_LD32(s_tmem + half * 64 + 32, s[1]);
-                tc_wait_ld();
-                TC_LAP(1)
-                if (!(c_lo <= 0 && c_hi >= 63)) {
-                    #pragma unroll
-                    for (int q2 = 0; q2 < 2; ++q2) {
+                const bool full = c_lo <= 0 && c_hi >= kTileKeys - 1;
+                // Pass 1: the row maximum, 64 columns at a time (exact under any association).
+                float m = neg_inf;
+                #pragma unroll
+                for (int hb = 0; hb < 2; ++hb) {
+                    uint32_t s[2][32];
+                    HC_TMEM_LD32(s_tmem + hb * 64, s[0]);
+                    HC_TMEM_LD32(s_tmem + hb * 64 + 32, s[1]);
+                    tc_wait_ld();
+                    if (!full) {
                         #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int col = q2 * 32 + i;
-                            if (col < c_lo || col > c_hi) s[q2][i] = __float_as_uint(neg_inf);
+                        for (int idx = 0; idx < 64; ++idx) {
+                            const int col = hb * 64 + idx;
+                            if (col < c_lo || col > c_hi) s[idx >> 5][idx & 31] = __float_as_uint(neg_inf);
                         }
                     }
-                }
-                // Maximum of this half (exact under any association), then of the row through shared memory.
-                float mx[4];
-                #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    float acc = __uint_as_float(s[0][u]);
+                    float mx[4];
                     #pragma unroll
-                    for (int k = 1; k < 15; k += 2) {
-                        const int i0 = u + 4 * k, i1 = u + 4 * (k + 1);
-                        acc = fmax3(acc, __uint_as_float(s[i0 >> 5][i0 & 31]), __uint_as_float(s[i1 >> 5][i1 & 31]));
+                    for (int u = 0; u < 4; ++u) {
+                        float acc = __uint_as_float(s[0][u]);
+                        #pragma unroll
+                        for (int k = 1; k < 15; k += 2) {
+                            const int i0 = u + 4 * k, i1 = u + 4 * (k + 1);
+                            acc = fmax3(acc, __uint_as_float(s[i0 >> 5][i0 & 31]), __uint_as_float(s[i1 >> 5][i1 & 31]));
+                        }
+                        mx[u] = fmaxf(acc, __uint_as_float(s[1][28 + u]));
                     }
-                    mx[u] = fmaxf(acc, __uint_as_float(s[1][28 + u]));
+                    m = fmax3(m, fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
                 }
-                const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-                bars->xmax[sb][half][row] = m_half;
-                mbar_arrive(&bars->x_bar[quad]);             // the two warps that share this quadrant
-                if (!mbar_wait(&bars->x_bar[quad], xuse & 1, abort_flag, args.status, 11)) { ok = false; break; }
-                ++xuse;
-                const float m = fmaxf(m_half, bars->xmax[sb][half ^ 1][row]);
                 const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
                 TC_LAP(2)
-                uint32_t packed[32];
-                #pragma unroll
-                for (int q2 = 0; q2 < 2; ++q2) {
-                    #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float e0 = tile_weight_raw(__uint_as_float(s[q2][2 * i]), neg_mc, args.c);
-                        const float e1 = tile_weight_raw(__uint_as_float(s[q2][2 * i + 1]), neg_mc, args.c);
-                        packed[q2 * 16 + i] = pack_bf16x2(e0, e1);
+                if ((threadIdx.x & 127) == 0) TC_EVT(t, 6)
+                // The exp2 unit is the scarce resource of this kernel: the two groups enter pass 2
+                // strictly in turn (group 0 first), which keeps them half a period apart instead of
+                // colliding in it and idling together.
+                const uint32_t own = t >> 1;                 // ordinal of this tile among the group's tiles
+                if (take_turns && (parity == 1 || own > 0)) {
+                    if (!mbar_wait(&bars->xu_turn[parity], (parity == 1 ? own : own - 1) & 1, abort_flag, args.status, 11)) {
+                        ok = false;
+                        break;
                     }
-                    HC_TMEM_ST16(s_tmem + half * 32 + q2 * 16, (&packed[q2 * 16]));
                 }
-                if (!LT::kSumOnTensor) {
-                    // Sum of this half's 64 weights: two groups of 32, each by the butterfly tree
-                    // (i with i + 16, then + 8, + 4, + 2, + 1), then the two groups added.
+                TC_LAP(1)
+                if ((threadIdx.x & 127) == 0) TC_EVT(t, 7)
+                // Pass 2: the weights, 64 columns at a time; P overwrites S columns already consumed
+                // (the bf16 weights of columns 64 h .. 64 h + 63 land in 32-bit columns 32 h .. 32 h + 31).
+                float half_sum[2] = {0.0f, 0.0f};
+                #pragma unroll
+                for (int hb = 0; hb < 2; ++hb) {
+                    uint32_t s[2][32];
+                    HC_TMEM_LD32(s_tmem + hb * 64, s[0]);
+                    HC_TMEM_LD32(s_tmem + hb * 64 + 32, s[1]);
+                    tc_wait_ld();
+                    if (!full) {
+                        #pragma unroll
+                        for (int idx = 0; idx < 64; ++idx) {
+                            const int col = hb * 64 + idx;
+                            if (col < c_lo || col > c_hi) s[idx >> 5][idx & 31] = __float_as_uint(neg_inf);
+                        }
+                    }
                     float part[2];
                     #pragma unroll
                     for (int q2 = 0; q2 < 2; ++q2) {
-                        float a[16];
+                        uint32_t packed[16];
                         #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            const uint32_t lo_word = packed[q2 * 16 + (i >> 1)], hi_word = packed[q2 * 16 + ((i + 16) >> 1)];
-                            const float x = __uint_as_float((i & 1) ? (lo_word & 0xffff0000u) : (lo_word << 16));
-                            const float y = __uint_as_float((i & 1) ? (hi_word & 0xffff0000u) : (hi_word << 16));
-                            a[i] = __fadd_rn(x, y);
+                            const float e0 = tile_weight_raw(__uint_as_float(s[q2][2 * i]), neg_mc, args.c);
+                            const float e1 = tile_weight_raw(__uint_as_float(s[q2][2 * i + 1]), neg_mc, args.c);
+                            packed[i] = pack_bf16x2(e0, e1);
                         }
-                        #pragma unroll
-                        for (int i = 0; i < 8; ++i) a[i] = __fadd_rn(a[i], a[i + 8]);
-                        #pragma unroll
-                        for (int i = 0; i < 4; ++i) a[i] = __fadd_rn(a[i], a[i + 4]);
-                        a[0] = __fadd_rn(a[0], a[2]);
-                        a[1] = __fadd_rn(a[1], a[3]);
-                        part[q2] = __fadd_rn(a[0], a[1]);
+                        HC_TMEM_ST16(s_tmem + hb * 32 + q2 * 16, packed);
+                        if (!LT::kSumOnTensor) {
+                            // Sum of a group of 32 weights by the butterfly tree (i with i + 16, then
+                            // + 8, + 4, + 2, + 1); a half is its two groups added, the row its two halves.
+                            float a[16];
+                            #pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const uint32_t lo_word = packed[i >> 1], hi_word = packed[(i + 16) >> 1];
+                                const float x = __uint_as_float((i & 1) ? (lo_word & 0xffff0000u) : (lo_word << 16));
+                                const float y = __uint_as_float((i & 1) ? (hi_word & 0xffff0000u) : (hi_word << 16));
+                                a[i] = __fadd_rn(x, y);
+                            }
+                            #pragma unroll
+                            for (int i = 0; i < 8; ++i) a[i] = __fadd_rn(a[i], a[i + 8]);
+                            #pragma unroll
+                            for (int i = 0; i < 4; ++i) a[i] = __fadd_rn(a[i], a[i + 4]);
+                            a[0] = __fadd_rn(a[0], a[2]);
+                            a[1] = __fadd_rn(a[1], a[3]);
+                            part[q2] = __fadd_rn(a[0], a[1]);
+                        }
                     }
-                    bars->l[t & 3][half][row] = __fadd_rn(part[0], part[1]);
+                    if (!LT::kSumOnTensor) half_sum[hb] = __fadd_rn(part[0], part[1]);
                 }
-                if (half == 0) bars->mm[t & 3][row] = __fmul_rn(m, args.c);
+                if (take_turns) mbar_arrive(&bars->xu_turn[parity ^ 1]);
+                if (!LT::kSumOnTensor) bars->l[t & 3][row] = __fadd_rn(half_sum[0], half_sum[1]);
+                bars->mm[t & 3][row] = __fmul_rn(m, args.c);
                 TC_LAP(3)
+                if ((threadIdx.x & 127) == 0) TC_EVT(t, 8)
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[sb]);
                 TC_LAP(4)
-                if (threadIdx.x == 128) TC_TRACE(6);
+                if ((threadIdx.x & 127) == 0) TC_EVT(t, 9)
             }
         }
         if (threadIdx.x == 128) { TC_LAP_STORE(1) }
@@ -523,7 +542,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 tc_wait_ld();
                 return __uint_as_float(bits);
             }
-            return __fadd_rn(bars->l[t & 3][0][row], bars->l[t & 3][1][row]);
+            return bars->l[t & 3][row];
         };
         uint32_t t = 0, it = 0;
         bool ok = true;
@@ -563,6 +582,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 if (!mbar_wait(&bars->o_full[ob], (t / LT::kOBufs) & 1, abort_flag, args.status, 9)) { ok = false; break; }
                 TC_LAP(0)
                 if (threadIdx.x == 384) TC_TRACE(7);
+                if (threadIdx.x == 384) TC_EVT(t, 10)
                 tc_fence_after();
                 if (!warp_has_rows) {
                     tc_fence_before();
@@ -627,6 +647,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     }
                 }
                 TC_LAP(2)
+                if (threadIdx.x == 384) TC_EVT(t, 11)
             }
             if (!ok) break;
             if (valid && !args.decode) {
