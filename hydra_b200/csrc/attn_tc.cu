@@ -50,13 +50,18 @@ struct TcLayout {
     static constexpr int kBlocks = D / 64;                   // 64-element (128-byte) column blocks
     static constexpr int kTileBytes = kTileKeys * D * 2;     // one K or V tile
     static constexpr int kStages = D == 64 ? 4 : 2;
-    static constexpr int kOBufs = 2;
+    static constexpr int kSBufs = 3;                         // S / P buffers of 128 columns at 0, 128, 256
     static constexpr int kQBytes = kRows * D * 2;            // one Q tile; two are kept
-    static constexpr int kSCol0 = 0, kSCol1 = 128;
-    static constexpr int kOCol0 = 256;
-    // d = 64 leaves room beside each O buffer for 16 columns of row sums computed by the tensor core.
+    static constexpr int kOCol0 = kSBufs * kTileKeys;        // the one O buffer
+    // d = 64 leaves room beside O for 16 columns of row sums computed by the tensor core.
     static constexpr bool kSumOnTensor = D == 64;
-    static constexpr int kOStride = kSumOnTensor ? D + 16 : D;
+    // Registers per thread after setmaxnreg (control / softmax / fold); 128 x their sum with the
+    // softmax counted twice is the 64 K register file.
+    // With d = 64 the fold needs less and a softmax thread can hold its whole row of S.
+    static constexpr bool kRowInRegs = D == 64;
+    static constexpr int kRegsControl = 48;
+    static constexpr int kRegsSoftmax = kRowInRegs ? 152 : 112;
+    static constexpr int kRegsFold = kRowInRegs ? 160 : 232;
     static constexpr int kTmemCols = 512;
     static constexpr int kOnesBytes = kTileKeys * 128;       // a 128-row block of bf16 1.0 (16 KiB)
     static constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + 2 * kStages * kTileBytes + kOnesBytes;
@@ -65,12 +70,13 @@ struct TcLayout {
 struct TcBarriers {
     uint64_t q_full[2], q_empty[2];
     uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
-    uint64_t s_full[2], p_full[2], o_full[2], o_free[2];
+    uint64_t s_full[3], p_full[3], pv_done[3];   // per S buffer; pv_done: P V has read the buffer's P
+    uint64_t o_full, o_free;
     uint64_t xu_turn[2];      // the softmax warpgroups take turns in the exp2 phase
     uint32_t tmem_base;
     int abort_flag;
-    float mm[4][kRows];       // per-tile scaled maxima, softmax -> fold (ring of 4 tiles)
-    float l[4][kRows];        // per-tile row sums (when not summed on the tensor core)
+    float mm[8][kRows];       // per-tile scaled maxima, softmax -> fold (ring of 8 tiles)
+    float l[8][kRows];        // per-tile row sums (when not summed on the tensor core)
 };
 
 // One unit of work of a CTA.
@@ -90,11 +96,11 @@ __device__ __forceinline__ void tc_trace(int slot) {
 // Clock stamps of the events of stream tiles 16..23 of CTA 0 (rows 200..207 of the timeline plane).
 #define TC_EVT(t, id) { if (blockIdx.x == 0 && (t) >= 16u && (t) < 24u) hc_tc_trace[(200 + (t) - 16) * 16 + (id)] = (unsigned long long)clock64(); }
 #else
-#define TC_EVT(t, id)
+#define TC_EVT(t, id) {}
 #define TC_TRACE(slot)
 #define TC_LAP_DECL
-#define TC_LAP(k)
-#define TC_LAP_STORE(base)
+#define TC_LAP(k) {}
+#define TC_LAP_STORE(base) {}
 #endif
 
 template <int D>
@@ -122,12 +128,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars->q_full[i], 128);
             mbar_init(&bars->q_empty[i], 1);
-            mbar_init(&bars->s_full[i], 1);
-            mbar_init(&bars->p_full[i], 128);
-            mbar_init(&bars->o_full[i], 1);
-            mbar_init(&bars->o_free[i], 128);
             mbar_init(&bars->xu_turn[i], 128);
         }
+        for (int i = 0; i < 3; ++i) {
+            mbar_init(&bars->s_full[i], 1);
+            mbar_init(&bars->p_full[i], 128);
+            mbar_init(&bars->pv_done[i], 1);
+        }
+        mbar_init(&bars->o_full, 1);
+        mbar_init(&bars->o_free, 128);
         for (int i = 0; i < 4; ++i) {
             mbar_init(&bars->k_full[i], 1);
             mbar_init(&bars->k_empty[i], 1);
@@ -156,7 +165,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     // Registers follow the work (setmaxnreg, first thing in each warpgroup's branch): the fold
     // warpgroup holds a row of O per thread, the control warpgroup needs almost none.
     if (wg == 0) {
-    reg_dealloc<48>();
+    reg_dealloc<LT::kRegsControl>();
     if (warp == 0) {
         // ===== producer: one stream of tiles across all of this CTA's items =====
         if (lane == 0) {
@@ -192,109 +201,100 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             }
         }
     } else if (warp == 1) {
-        // ===== MMA issuer.  Two S tiles are always in flight, one per softmax warpgroup: S(t + 2) is
-        // queued right behind P V(t), which frees the buffer they share; item boundaries do not
-        // interrupt the stream.  The whole warp walks the loop and waits, so control flow stays
-        // warp-uniform; one elected lane issues the tcgen05 instructions. =====
-        {
-            constexpr uint32_t idesc_qk = instr_desc(kTileKeys, false);
-            // With the row sums on the tensor core, P V and P x ones are one instruction: the B operand
-            // is the V tile (64 columns) followed by a block of ones that the descriptor's
-            // column-block stride points at, so O gets 16 more columns, each the row's sum.
-            constexpr uint32_t idesc_pv = instr_desc(LT::kSumOnTensor ? D + 16 : D, true);
-            const uint32_t ones_addr = smem_u32(ones_smem);
-            const uint32_t v_base = smem_u32(v_smem);
-            const uint64_t q_desc0 = smem_desc(smem_u32(q_smem), 16);
-            const uint64_t k_desc0 = smem_desc(smem_u32(k_smem), 16);
-            TC_LAP_DECL
-            // S = Q K^T of the tile under the cursor.
-            auto issue_qk = [&](const TcCursor& c) -> bool {
-                const int slot = int(c.t % LT::kStages);
-                const int qb = int(c.it & 1);
-                const int sb = int(c.t & 1);
-                if (c.j == 0 && !mbar_wait(&bars->q_full[qb], (c.it >> 1) & 1, abort_flag, args.status, 4)) return false;
-                if (!mbar_wait(&bars->k_full[slot], (c.t / LT::kStages) & 1, abort_flag, args.status, 3)) return false;
-                tc_fence_after();
-                TC_LAP(0)
-                TC_EVT(c.t - 2, 3)
-                if (elect_one()) {
-                    // Descriptors differ from the precomputed bases only in the 16-byte address field.
-                    const uint64_t q_desc = q_desc0 + uint64_t((qb * LT::kQBytes) >> 4);
-                    const uint64_t k_desc = k_desc0 + uint64_t((slot * LT::kTileBytes) >> 4);
-                    const uint32_t s_tmem = tmem + (sb ? LT::kSCol1 : LT::kSCol0);
+        // ===== S issuer: S = Q K^T, up to three tiles ahead of the softmax, across item boundaries.
+        // The whole warp walks the loop and waits, so control flow stays warp-uniform; one elected
+        // lane issues the tcgen05 instructions. =====
+        constexpr uint32_t idesc_qk = instr_desc(kTileKeys, false);
+        const uint64_t q_desc0 = smem_desc(smem_u32(q_smem), 16);
+        const uint64_t k_desc0 = smem_desc(smem_u32(k_smem), 16);
+        TC_LAP_DECL
+        for (TcCursor c = cursor_begin(args); cursor_valid(args, c); cursor_advance(args, c)) {
+            const uint32_t t = c.t;
+            const int slot = int(t % LT::kStages);
+            const int qb = int(c.it & 1);
+            const int sb = int(t % LT::kSBufs);
+            // The buffer's previous contents, P of tile t - 3, must have been consumed.
+            if (t >= LT::kSBufs &&
+                !mbar_wait(&bars->pv_done[sb], (t / LT::kSBufs - 1) & 1, abort_flag, args.status, 12)) break;
+            if (c.j == 0 && !mbar_wait(&bars->q_full[qb], (c.it >> 1) & 1, abort_flag, args.status, 4)) break;
+            if (!mbar_wait(&bars->k_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 3)) break;
+            tc_fence_after();
+            TC_LAP(0)
+            TC_EVT(t, 3)
+            if (elect_one()) {
+                // Descriptors differ from the precomputed bases only in the 16-byte address field.
+                const uint64_t q_desc = q_desc0 + uint64_t((qb * LT::kQBytes) >> 4);
+                const uint64_t k_desc = k_desc0 + uint64_t((slot * LT::kTileBytes) >> 4);
+                const uint32_t s_tmem = tmem + sb * kTileKeys;
+                #pragma unroll
+                for (int b = 0; b < LT::kBlocks; ++b) {
                     #pragma unroll
-                    for (int b = 0; b < LT::kBlocks; ++b) {
-                        #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) {
-                            const uint64_t off = uint64_t((b * (kRows * 128) + ks * 32) >> 4);
-                            mma_ss(s_tmem, q_desc + off, k_desc + off, idesc_qk, (b | ks) != 0 ? 1u : 0u);
-                        }
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t off = uint64_t((b * (kRows * 128) + ks * 32) >> 4);
+                        mma_ss(s_tmem, q_desc + off, k_desc + off, idesc_qk, (b | ks) != 0 ? 1u : 0u);
                     }
-                    TC_LAP(1)
-                    tc_commit(&bars->k_empty[slot]);
-                    tc_commit(&bars->s_full[sb]);
-                    if (c.j + 1 == c.w.n_tiles) tc_commit(&bars->q_empty[qb]);   // the item's Q tile was read for the last time
-                    TC_LAP(2)
                 }
-                __syncwarp();
-                TC_EVT(c.t - 2, 4)
-                return true;
-            };
-            TcCursor ahead = cursor_begin(args);
-            bool ok = true;
-            for (int n = 0; ok && n < 2 && cursor_valid(args, ahead); ++n) {
-                ok = issue_qk(ahead);
-                cursor_advance(args, ahead);
+                TC_LAP(1)
+                tc_commit(&bars->k_empty[slot]);
+                tc_commit(&bars->s_full[sb]);
+                if (c.j + 1 == c.w.n_tiles) tc_commit(&bars->q_empty[qb]);   // the item's Q tile was read for the last time
+                TC_LAP(2)
             }
-            for (TcCursor c = cursor_begin(args); ok && cursor_valid(args, c); cursor_advance(args, c)) {
-                const uint32_t t = c.t;
+            __syncwarp();
+            TC_EVT(t, 4)
+        }
+        if (elect_one()) { TC_LAP_STORE(3) }
+    } else if (warp == 2) {
+        // ===== O issuer: O_t = P_t V_t (A = P from tensor memory) as soon as the tile's weights are
+        // written and the fold has taken the previous tile out of the O buffer. =====
+        // With the row sums on the tensor core, P V and P x ones are one instruction: the B operand
+        // is the V tile (64 columns) followed by a block of ones that the descriptor's
+        // column-block stride points at, so O gets 16 more columns, each the row's sum.
+        constexpr uint32_t idesc_pv = instr_desc(LT::kSumOnTensor ? D + 16 : D, true);
+        const uint32_t ones_addr = smem_u32(ones_smem);
+        const uint32_t v_base = smem_u32(v_smem);
+        uint32_t t = 0;
+        bool ok = true;
+        for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item)) {
+            const int n_tiles = decode_item(args, item).n_tiles;
+            for (int j = 0; j < n_tiles; ++j, ++t) {
                 const int slot = int(t % LT::kStages);
-                const int ob = int(t % LT::kOBufs);
-                if (!mbar_wait(&bars->p_full[t & 1], (t >> 1) & 1, abort_flag, args.status, 5)) break;
+                const int sb = int(t % LT::kSBufs);
+                if (!mbar_wait(&bars->p_full[sb], (t / LT::kSBufs) & 1, abort_flag, args.status, 5)) { ok = false; break; }
                 TC_EVT(t, 0)
-                if (!mbar_wait(&bars->v_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 6)) break;
-                if (t >= LT::kOBufs &&
-                    !mbar_wait(&bars->o_free[ob], (t / LT::kOBufs - 1) & 1, abort_flag, args.status, 7)) break;
+                if (!mbar_wait(&bars->v_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 6)) { ok = false; break; }
+                if (t >= 1 && !mbar_wait(&bars->o_free, (t - 1) & 1, abort_flag, args.status, 7)) { ok = false; break; }
                 tc_fence_after();
-                TC_LAP(3)
                 TC_EVT(t, 1)
                 if (elect_one()) {
                     const uint32_t v_addr = v_base + slot * LT::kTileBytes;
-                    const uint32_t p_tmem = tmem + ((t & 1) ? LT::kSCol1 : LT::kSCol0);
-                    const uint32_t o_tmem = tmem + LT::kOCol0 + ob * LT::kOStride;
+                    const uint32_t p_tmem = tmem + sb * kTileKeys;
+                    const uint32_t o_tmem = tmem + LT::kOCol0;
                     const uint32_t block_stride = LT::kSumOnTensor ? ones_addr - v_addr : uint32_t(kTileKeys * 128);
                     const uint64_t v_desc = smem_desc(v_addr, block_stride);
                     #pragma unroll
                     for (int ks = 0; ks < kTileKeys / 16; ++ks) {
                         mma_ts(o_tmem, p_tmem + ks * 8, v_desc + uint64_t((ks * 2048) >> 4), idesc_pv, ks != 0 ? 1u : 0u);
                     }
-                    TC_LAP(4)
+                    tc_commit(&bars->o_full);
+                    tc_commit(&bars->pv_done[sb]);
                     tc_commit(&bars->v_empty[slot]);
-                    tc_commit(&bars->o_full[ob]);
-                    TC_LAP(5)
                 }
                 __syncwarp();
                 TC_EVT(t, 2)
-                if (cursor_valid(args, ahead)) {
-                    ok = issue_qk(ahead);
-                    cursor_advance(args, ahead);
-                }
             }
-            if (elect_one()) { TC_LAP_STORE(3) }
         }
     }
     } else if (wg == 1 || wg == 2) {
         // ===== softmax: warpgroup 1 takes the even tiles of the stream (S buffer 0), warpgroup 2 the
         // odd ones (S buffer 1), so one group's exp2 phase overlaps the other's wait, load and
         // maximum.  Thread = row; the row is read twice (maximum, then weights) to stay in registers. =====
-        reg_dealloc<112>();
+        if constexpr (LT::kRegsSoftmax > 128) reg_alloc<LT::kRegsSoftmax>(); else reg_dealloc<LT::kRegsSoftmax>();
         const int parity = wg - 1;
-        const int sb = parity;
         const int quad = warp & 3;                           // the TMEM lane quadrant this warp may touch
         const int row = quad * 32 + lane;
         const int t_local = row >> args.log_group;
         const uint32_t lane_base = uint32_t(quad * 32) << 16;
-        const uint32_t s_tmem = tmem + lane_base + (sb ? LT::kSCol1 : LT::kSCol0);
         const float neg_inf = __int_as_float(0xff800000);
         const bool take_turns = !(args.decode && LT::kSumOnTensor);
         uint32_t t = 0;
@@ -308,8 +308,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const int lo = args.window > 0 ? max(0, pos - args.window + 1) : 0;
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
                 if (int(t & 1) != parity) continue;
+                const int sb = int(t % LT::kSBufs);
+                const uint32_t s_tmem = tmem + lane_base + sb * kTileKeys;
                 TC_LAP(5)
-                if (!mbar_wait(&bars->s_full[sb], (t >> 1) & 1, abort_flag, args.status, 8)) { ok = false; break; }
+                if (!mbar_wait(&bars->s_full[sb], (t / LT::kSBufs) & 1, abort_flag, args.status, 8)) { ok = false; break; }
                 TC_LAP(0)
                 if ((threadIdx.x & 127) == 0) TC_EVT(t, 5)
                 tc_fence_after();
@@ -373,7 +375,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
                             m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
                             neg_mc[rs] = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
-                            if (q4 == 0) bars->mm[t & 3][(lane >> 2) + 8 * rs] = __fmul_rn(m, args.c);
+                            if (q4 == 0) bars->mm[t & 7][(lane >> 2) + 8 * rs] = __fmul_rn(m, args.c);
                         }
                     }
                     TC_LAP(2)
@@ -405,40 +407,121 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 const int c_lo = lo - key0;                  // visible columns: [c_lo, c_hi]
                 const int c_hi = pos - key0;
                 const bool full = c_lo <= 0 && c_hi >= kTileKeys - 1;
-                // Pass 1: the row maximum, 64 columns at a time (exact under any association).
-                float m = neg_inf;
-                #pragma unroll
-                for (int hb = 0; hb < 2; ++hb) {
-                    uint32_t s[2][32];
-                    HC_TMEM_LD32(s_tmem + hb * 64, s[0]);
-                    HC_TMEM_LD32(s_tmem + hb * 64 + 32, s[1]);
+                if constexpr (LT::kRowInRegs) {
+                    // The whole row of S in registers: one load, the maximum, the scaled differences
+                    // (two per instruction), and only then, in this group's turn, the exp2 unit's
+                    // share: exp2, rounding to bf16 and the store of P.
+                    uint32_t s[4][32];
+                    HC_TMEM_LD32(s_tmem, s[0]);
+                    HC_TMEM_LD32(s_tmem + 32, s[1]);
+                    HC_TMEM_LD32(s_tmem + 64, s[2]);
+                    HC_TMEM_LD32(s_tmem + 96, s[3]);
                     tc_wait_ld();
                     if (!full) {
                         #pragma unroll
-                        for (int idx = 0; idx < 64; ++idx) {
-                            const int col = hb * 64 + idx;
-                            if (col < c_lo || col > c_hi) s[idx >> 5][idx & 31] = __float_as_uint(neg_inf);
+                        for (int col = 0; col < kTileKeys; ++col) {
+                            if (col < c_lo || col > c_hi) s[col >> 5][col & 31] = __float_as_uint(neg_inf);
                         }
                     }
-                    float mx[4];
+                    float mx[8];
                     #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
+                    for (int u = 0; u < 8; ++u) {
                         float acc = __uint_as_float(s[0][u]);
                         #pragma unroll
                         for (int k = 1; k < 15; k += 2) {
-                            const int i0 = u + 4 * k, i1 = u + 4 * (k + 1);
+                            const int i0 = u + 8 * k, i1 = u + 8 * (k + 1);
                             acc = fmax3(acc, __uint_as_float(s[i0 >> 5][i0 & 31]), __uint_as_float(s[i1 >> 5][i1 & 31]));
                         }
-                        mx[u] = fmaxf(acc, __uint_as_float(s[1][28 + u]));
+                        mx[u] = fmaxf(acc, __uint_as_float(s[3][24 + u]));
                     }
-                    m = fmax3(m, fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                    const float m = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmax3(fmaxf(mx[3], mx[4]), fmaxf(mx[5], mx[6]), mx[7]));
+                    const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
+                    #pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) fma2_inplace(s[q][2 * i], s[q][2 * i + 1], args.c, neg_mc);
+                    }
+                    TC_LAP(2)
+                    if ((threadIdx.x & 127) == 0) TC_EVT(t, 6)
+                    const uint32_t own = t >> 1;             // ordinal of this tile among the group's tiles
+                    if (take_turns && (parity == 1 || own > 0)) {
+                        if (!mbar_wait(&bars->xu_turn[parity], (parity == 1 ? own : own - 1) & 1, abort_flag, args.status, 11)) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    TC_LAP(1)
+                    if ((threadIdx.x & 127) == 0) TC_EVT(t, 7)
+                    #pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        #pragma unroll
+                        for (int i = 0; i < 32; ++i) s[q][i] = __float_as_uint(ex2(__uint_as_float(s[q][i])));
+                        uint32_t packed[16];
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            packed[i] = pack_bf16x2(__uint_as_float(s[q][2 * i]), __uint_as_float(s[q][2 * i + 1]));
+                        }
+                        HC_TMEM_ST16(s_tmem + q * 16, packed);
+                    }
+                    if (take_turns) mbar_arrive(&bars->xu_turn[parity ^ 1]);
+                    bars->mm[t & 7][row] = __fmul_rn(m, args.c);
+                    TC_LAP(3)
+                    if ((threadIdx.x & 127) == 0) TC_EVT(t, 8)
+                    tc_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(&bars->p_full[sb]);
+                    TC_LAP(4)
+                    if ((threadIdx.x & 127) == 0) TC_EVT(t, 9)
+                    if (lane == 0) TC_EVT(t, 12 + quad)
+                    continue;
+                }
+                // The row is read twice, 32 columns at a time, in rolled loops: the maximum, then the
+                // weights.  Rolled on purpose: the loop bodies of the four roles have to stay resident
+                // in the instruction cache together.  Each load is in flight while the previous group
+                // is worked on.  P overwrites S columns already consumed (the bf16 weights of columns
+                // 32 q .. 32 q + 31 land in 32-bit columns 16 q .. 16 q + 15).
+                auto mask_group = [&](uint32_t (&s)[32], int base_col) {
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int col = base_col + i;
+                        if (col < c_lo || col > c_hi) s[i] = __float_as_uint(neg_inf);
+                    }
+                };
+                auto group_max = [&](const uint32_t (&s)[32]) -> float {
+                    float mx[4];
+                    #pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        float acc = __uint_as_float(s[u]);
+                        #pragma unroll
+                        for (int k = 1; k < 7; k += 2) {
+                            acc = fmax3(acc, __uint_as_float(s[u + 4 * k]), __uint_as_float(s[u + 4 * (k + 1)]));
+                        }
+                        mx[u] = fmaxf(acc, __uint_as_float(s[u + 28]));
+                    }
+                    return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                };
+                float m = neg_inf;
+                {
+                    uint32_t cur[32], nxt[32];
+                    HC_TMEM_LD32(s_tmem, cur);
+                    tc_wait_ld();
+                    #pragma unroll 1
+                    for (int h = 0; h < 2; ++h) {
+                        HC_TMEM_LD32(s_tmem + 64 * h + 32, nxt);
+                        if (!full) mask_group(cur, 64 * h);
+                        m = fmaxf(m, group_max(cur));
+                        tc_wait_ld();
+                        if (h == 0) HC_TMEM_LD32(s_tmem + 64, cur);
+                        if (!full) mask_group(nxt, 64 * h + 32);
+                        m = fmaxf(m, group_max(nxt));
+                        tc_wait_ld();
+                    }
                 }
                 const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
                 TC_LAP(2)
                 if ((threadIdx.x & 127) == 0) TC_EVT(t, 6)
-                // The exp2 unit is the scarce resource of this kernel: the two groups enter pass 2
-                // strictly in turn (group 0 first), which keeps them half a period apart instead of
-                // colliding in it and idling together.
+                // The two groups enter the weights pass strictly in turn (group 0 first), which keeps
+                // them half a period apart instead of colliding in it and idling together.
                 const uint32_t own = t >> 1;                 // ordinal of this tile among the group's tiles
                 if (take_turns && (parity == 1 || own > 0)) {
                     if (!mbar_wait(&bars->xu_turn[parity], (parity == 1 ? own : own - 1) & 1, abort_flag, args.status, 11)) {
@@ -448,58 +531,57 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 }
                 TC_LAP(1)
                 if ((threadIdx.x & 127) == 0) TC_EVT(t, 7)
-                // Pass 2: the weights, 64 columns at a time; P overwrites S columns already consumed
-                // (the bf16 weights of columns 64 h .. 64 h + 63 land in 32-bit columns 32 h .. 32 h + 31).
-                float half_sum[2] = {0.0f, 0.0f};
-                #pragma unroll
-                for (int hb = 0; hb < 2; ++hb) {
-                    uint32_t s[2][32];
-                    HC_TMEM_LD32(s_tmem + hb * 64, s[0]);
-                    HC_TMEM_LD32(s_tmem + hb * 64 + 32, s[1]);
-                    tc_wait_ld();
-                    if (!full) {
-                        #pragma unroll
-                        for (int idx = 0; idx < 64; ++idx) {
-                            const int col = hb * 64 + idx;
-                            if (col < c_lo || col > c_hi) s[idx >> 5][idx & 31] = __float_as_uint(neg_inf);
-                        }
-                    }
-                    float part[2];
+                // Weights of one group of 32 columns; returns their sum when the tensor core does not.
+                auto group_weights = [&](const uint32_t (&s)[32], uint32_t dst) -> float {
+                    uint32_t packed[16];
                     #pragma unroll
-                    for (int q2 = 0; q2 < 2; ++q2) {
-                        uint32_t packed[16];
-                        #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const float e0 = tile_weight_raw(__uint_as_float(s[q2][2 * i]), neg_mc, args.c);
-                            const float e1 = tile_weight_raw(__uint_as_float(s[q2][2 * i + 1]), neg_mc, args.c);
-                            packed[i] = pack_bf16x2(e0, e1);
-                        }
-                        HC_TMEM_ST16(s_tmem + hb * 32 + q2 * 16, packed);
-                        if (!LT::kSumOnTensor) {
-                            // Sum of a group of 32 weights by the butterfly tree (i with i + 16, then
-                            // + 8, + 4, + 2, + 1); a half is its two groups added, the row its two halves.
-                            float a[16];
-                            #pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                const uint32_t lo_word = packed[i >> 1], hi_word = packed[(i + 16) >> 1];
-                                const float x = __uint_as_float((i & 1) ? (lo_word & 0xffff0000u) : (lo_word << 16));
-                                const float y = __uint_as_float((i & 1) ? (hi_word & 0xffff0000u) : (hi_word << 16));
-                                a[i] = __fadd_rn(x, y);
-                            }
-                            #pragma unroll
-                            for (int i = 0; i < 8; ++i) a[i] = __fadd_rn(a[i], a[i + 8]);
-                            #pragma unroll
-                            for (int i = 0; i < 4; ++i) a[i] = __fadd_rn(a[i], a[i + 4]);
-                            a[0] = __fadd_rn(a[0], a[2]);
-                            a[1] = __fadd_rn(a[1], a[3]);
-                            part[q2] = __fadd_rn(a[0], a[1]);
-                        }
+                    for (int i = 0; i < 16; ++i) {
+                        const float e0 = tile_weight_raw(__uint_as_float(s[2 * i]), neg_mc, args.c);
+                        const float e1 = tile_weight_raw(__uint_as_float(s[2 * i + 1]), neg_mc, args.c);
+                        packed[i] = pack_bf16x2(e0, e1);
                     }
-                    if (!LT::kSumOnTensor) half_sum[hb] = __fadd_rn(part[0], part[1]);
+                    HC_TMEM_ST16(dst, packed);
+                    if (LT::kSumOnTensor) return 0.0f;
+                    // Sum of the 32 weights by the butterfly tree (i with i + 16, then + 8, + 4, + 2, + 1).
+                    float a[16];
+                    #pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t lo_word = packed[i >> 1], hi_word = packed[(i + 16) >> 1];
+                        const float x = __uint_as_float((i & 1) ? (lo_word & 0xffff0000u) : (lo_word << 16));
+                        const float y = __uint_as_float((i & 1) ? (hi_word & 0xffff0000u) : (hi_word << 16));
+                        a[i] = __fadd_rn(x, y);
+                    }
+                    #pragma unroll
+                    for (int i = 0; i < 8; ++i) a[i] = __fadd_rn(a[i], a[i + 8]);
+                    #pragma unroll
+                    for (int i = 0; i < 4; ++i) a[i] = __fadd_rn(a[i], a[i + 4]);
+                    a[0] = __fadd_rn(a[0], a[2]);
+                    a[1] = __fadd_rn(a[1], a[3]);
+                    return __fadd_rn(a[0], a[1]);
+                };
+                // A half of the row is its two groups added, the row its two halves.
+                float half_sum[2] = {0.0f, 0.0f};
+                {
+                    uint32_t cur[32], nxt[32];
+                    HC_TMEM_LD32(s_tmem, cur);
+                    tc_wait_ld();
+                    #pragma unroll 1
+                    for (int h = 0; h < 2; ++h) {
+                        HC_TMEM_LD32(s_tmem + 64 * h + 32, nxt);
+                        if (!full) mask_group(cur, 64 * h);
+                        const float g0 = group_weights(cur, s_tmem + 32 * h);
+                        tc_wait_ld();
+                        if (h == 0) HC_TMEM_LD32(s_tmem + 64, cur);
+                        if (!full) mask_group(nxt, 64 * h + 32);
+                        const float g1 = group_weights(nxt, s_tmem + 32 * h + 16);
+                        tc_wait_ld();
+                        const float hs = __fadd_rn(g0, g1);
+                        if (h == 0) half_sum[0] = hs; else half_sum[1] = hs;
+                    }
                 }
                 if (take_turns) mbar_arrive(&bars->xu_turn[parity ^ 1]);
-                if (!LT::kSumOnTensor) bars->l[t & 3][row] = __fadd_rn(half_sum[0], half_sum[1]);
-                bars->mm[t & 3][row] = __fmul_rn(m, args.c);
+                if (!LT::kSumOnTensor) bars->l[t & 7][row] = __fadd_rn(half_sum[0], half_sum[1]);
+                bars->mm[t & 7][row] = __fmul_rn(m, args.c);
                 TC_LAP(3)
                 if ((threadIdx.x & 127) == 0) TC_EVT(t, 8)
                 tc_wait_st();
@@ -512,7 +594,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         if (threadIdx.x == 128) { TC_LAP_STORE(1) }
     } else {
         // ===== fold + epilogue: thread = row; also stages the Q tiles =====
-        reg_alloc<232>();
+        reg_alloc<LT::kRegsFold>();
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int t_local = row >> args.log_group;
@@ -542,7 +624,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 tc_wait_ld();
                 return __uint_as_float(bits);
             }
-            return bars->l[t & 3][row];
+            return bars->l[t & 7][row];
         };
         uint32_t t = 0, it = 0;
         bool ok = true;
@@ -577,19 +659,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             #pragma unroll
             for (int i = 0; i < D; ++i) A[i] = 0.0f;
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
-                const int ob = int(t % LT::kOBufs);
                 TC_LAP(5)
-                if (!mbar_wait(&bars->o_full[ob], (t / LT::kOBufs) & 1, abort_flag, args.status, 9)) { ok = false; break; }
+                if (!mbar_wait(&bars->o_full, t & 1, abort_flag, args.status, 9)) { ok = false; break; }
                 TC_LAP(0)
                 if (threadIdx.x == 384) TC_TRACE(7);
                 if (threadIdx.x == 384) TC_EVT(t, 10)
                 tc_fence_after();
                 if (!warp_has_rows) {
                     tc_fence_before();
-                    mbar_arrive(&bars->o_free[ob]);
+                    mbar_arrive(&bars->o_free);
                     continue;
                 }
-                const uint32_t o_tmem = tmem + lane_base + LT::kOCol0 + ob * LT::kOStride;
+                const uint32_t o_tmem = tmem + lane_base + LT::kOCol0;
                 const float l_tile = tile_sum(o_tmem, t);
                 TC_LAP(1)
                 if (args.decode) {
@@ -603,7 +684,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         tc_wait_ld();
                         if (hb == D / 64 - 1) {
                             tc_fence_before();
-                            mbar_arrive(&bars->o_free[ob]);
+                            mbar_arrive(&bars->o_free);
                         }
                         if (valid) {
                             float* dst = args.part_o + prow * D + hb * 64;
@@ -618,13 +699,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         }
                     }
                     if (valid) {
-                        args.part_ml[prow * 2] = bars->mm[t & 3][row];
+                        args.part_ml[prow * 2] = bars->mm[t & 7][row];
                         args.part_ml[prow * 2 + 1] = l_tile;
                     }
                     continue;
                 }
                 float Mn, a, b;
-                fold_coefficients(M, bars->mm[t & 3][row], Mn, a, b);
+                fold_coefficients(M, bars->mm[t & 7][row], Mn, a, b);
                 L = __fmaf_rn(L, a, __fmul_rn(l_tile, b));
                 M = Mn;
                 #pragma unroll
@@ -635,7 +716,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     tc_wait_ld();
                     if (hb == D / 64 - 1) {
                         tc_fence_before();
-                        mbar_arrive(&bars->o_free[ob]);
+                        mbar_arrive(&bars->o_free);
                     }
                     #pragma unroll
                     for (int u = 0; u < 2; ++u) {

@@ -134,5 +134,15 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 
+// (x0, x1) <- (x0 * c + d, x1 * c + d), each rounded once, as one packed instruction.
+__device__ __forceinline__ void fma2_inplace(uint32_t& x0, uint32_t& x1, float c, float d) {
+    uint64_t x = uint64_t(x0) | (uint64_t(x1) << 32);
+    const uint64_t cc = uint64_t(__float_as_uint(c)) | (uint64_t(__float_as_uint(c)) << 32);
+    const uint64_t dd = uint64_t(__float_as_uint(d)) | (uint64_t(__float_as_uint(d)) << 32);
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(x) : "l"(x), "l"(cc), "l"(dd));
+    x0 = uint32_t(x);
+    x1 = uint32_t(x >> 32);
+}
+
 }  // namespace
 }  // namespace hc
