@@ -126,7 +126,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     if (threadIdx.x == 0) {
         TC_TRACE(0);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&bars->q_full[i], 128);
+            mbar_init(&bars->q_full[i], 1);
             mbar_init(&bars->q_empty[i], 1);
             mbar_init(&bars->xu_turn[i], 128);
         }
@@ -283,6 +283,46 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 __syncwarp();
                 TC_EVT(t, 2)
             }
+        }
+    } else {
+        // ===== Q stager: copies each item's Q tile (128 rows of the prepared q) into the swizzled
+        // K-major layout, up to two items ahead of the S issuer, so the global-memory latency of a
+        // new item never sits in another role's path.  Lane l copies rows l, l + 32, l + 64, l + 96. =====
+        uint32_t it = 0;
+        for (int item = first_item(args); item < args.n_items; item = next_item(args, item), ++it) {
+            const TcItem w = decode_item(args, item);
+            const int qb = int(it & 1);
+            // The buffer was last read by item it - 2.
+            if (it >= 2 && !mbar_wait(&bars->q_empty[qb], ((it >> 1) - 1) & 1, abort_flag, args.status, 10)) break;
+            unsigned char* dst = q_smem + qb * LT::kQBytes;
+            #pragma unroll 1
+            for (int r = 0; r < 4; ++r) {
+                const int row = r * 32 + lane;
+                const int t_local = row >> args.log_group;
+                const int g = row & (G - 1);
+                const bool valid = t_local < w.valid_tokens;
+                const uint16_t* src = args.q + (size_t(w.row0 + t_local) * args.q_heads + size_t(w.kv_head) * G + g) * D;
+                #pragma unroll
+                for (int b = 0; b < LT::kBlocks; ++b) {
+                    #pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        uint4 value[4];
+                        #pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            value[u] = make_uint4(0, 0, 0, 0);
+                            if (valid) value[u] = *reinterpret_cast<const uint4*>(src + b * 64 + (half * 4 + u) * 8);
+                        }
+                        #pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int ch = half * 4 + u;
+                            *reinterpret_cast<uint4*>(dst + b * (kRows * 128) + row * 128 + ((ch ^ (row & 7)) << 4)) = value[u];
+                        }
+                    }
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->q_full[qb]);
         }
     }
     } else if (wg == 1 || wg == 2) {
@@ -593,56 +633,26 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         }
         if (threadIdx.x == 128) { TC_LAP_STORE(1) }
     } else {
-        // ===== fold + epilogue: thread = row; also stages the Q tiles =====
+        // ===== fold + epilogue: thread = row =====
         reg_alloc<LT::kRegsFold>();
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int t_local = row >> args.log_group;
         const int g = row & (G - 1);
         const uint32_t lane_base = uint32_t(quad * 32) << 16;
-        // This thread copies its own row of an item's Q tile into the swizzled K-major layout.
-        auto stage_q = [&](const TcItem& w, int qb) {
-            const bool valid = t_local < w.valid_tokens;
-            const uint16_t* src = args.q + (size_t(w.row0 + t_local) * args.q_heads + size_t(w.kv_head) * G + g) * D;
-            unsigned char* dst = q_smem + qb * LT::kQBytes;
-            #pragma unroll
-            for (int b = 0; b < LT::kBlocks; ++b) {
-                #pragma unroll
-                for (int ch = 0; ch < 8; ++ch) {
-                    uint4 value = make_uint4(0, 0, 0, 0);
-                    if (valid) value = *reinterpret_cast<const uint4*>(src + b * 64 + ch * 8);
-                    *reinterpret_cast<uint4*>(dst + b * (kRows * 128) + row * 128 + ((ch ^ (row & 7)) << 4)) = value;
-                }
-            }
-            fence_proxy_async();
-            mbar_arrive(&bars->q_full[qb]);
-        };
         // The tile's row sum: from the tensor core (column D of the O buffer) or the two halves' sums.
-        auto tile_sum = [&](uint32_t o_tmem, uint32_t t) -> float {
-            if (LT::kSumOnTensor) {
-                const uint32_t bits = tmem_ld1(o_tmem + D);
-                tc_wait_ld();
-                return __uint_as_float(bits);
-            }
-            return bars->l[t & 7][row];
+        // Issued before the loads of O so that one wait covers both.
+        auto tile_sum = [&](uint32_t o_tmem, uint32_t t) -> uint32_t {
+            if (LT::kSumOnTensor) return tmem_ld1(o_tmem + D);
+            return __float_as_uint(bars->l[t & 7][row]);
         };
         uint32_t t = 0, it = 0;
         bool ok = true;
         int item = first_item(args);
         TC_LAP_DECL
-        if (item < args.n_items) stage_q(decode_item(args, item), 0);
         while (ok && item < args.n_items) {
             const TcItem w = decode_item(args, item);
             const int nxt = next_item(args, item);
-            if (nxt < args.n_items) {
-                // Stage the next item's Q now; its buffer was last read by item it - 1.
-                const int qb = int((it + 1) & 1);
-                if (it >= 1 && !mbar_wait(&bars->q_empty[qb], (((it + 1) >> 1) - 1) & 1, abort_flag, args.status, 10)) {
-                    ok = false;
-                    break;
-                }
-                stage_q(decode_item(args, nxt), qb);
-            }
             const int head = w.kv_head * G + g;
             const bool valid = t_local < w.valid_tokens;
             const bool warp_has_rows = quad * 32 < (w.valid_tokens << args.log_group);   // warp-uniform
@@ -671,7 +681,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     continue;
                 }
                 const uint32_t o_tmem = tmem + lane_base + LT::kOCol0;
-                const float l_tile = tile_sum(o_tmem, t);
+                const uint32_t l_bits = tile_sum(o_tmem, t);   // valid after the first wait below
                 TC_LAP(1)
                 if (args.decode) {
                     // Split decode: the tile's partial goes to the workspace; merge_tiles_kernel folds.
@@ -682,6 +692,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         HC_TMEM_LD32(o_tmem + hb * 64, o[0]);
                         HC_TMEM_LD32(o_tmem + hb * 64 + 32, o[1]);
                         tc_wait_ld();
+                        TC_LAP(2)
                         if (hb == D / 64 - 1) {
                             tc_fence_before();
                             mbar_arrive(&bars->o_free);
@@ -700,23 +711,26 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     }
                     if (valid) {
                         args.part_ml[prow * 2] = bars->mm[t & 7][row];
-                        args.part_ml[prow * 2 + 1] = l_tile;
+                        args.part_ml[prow * 2 + 1] = __uint_as_float(l_bits);
                     }
+                    TC_LAP(3)
                     continue;
                 }
                 float Mn, a, b;
-                fold_coefficients(M, bars->mm[t & 7][row], Mn, a, b);
-                L = __fmaf_rn(L, a, __fmul_rn(l_tile, b));
-                M = Mn;
                 #pragma unroll
                 for (int hb = 0; hb < D / 64; ++hb) {
                     uint32_t o[2][32];
                     HC_TMEM_LD32(o_tmem + hb * 64, o[0]);
                     HC_TMEM_LD32(o_tmem + hb * 64 + 32, o[1]);
+                    if (hb == 0) fold_coefficients(M, bars->mm[t & 7][row], Mn, a, b);   // while the loads fly
                     tc_wait_ld();
                     if (hb == D / 64 - 1) {
                         tc_fence_before();
                         mbar_arrive(&bars->o_free);
+                    }
+                    if (hb == 0) {
+                        L = __fmaf_rn(L, a, __fmul_rn(__uint_as_float(l_bits), b));
+                        M = Mn;
                     }
                     #pragma unroll
                     for (int u = 0; u < 2; ++u) {
