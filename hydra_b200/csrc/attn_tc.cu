@@ -11,20 +11,24 @@
 // TMA ring, tensor memory and barriers across items, so one item's ramp-up hides behind the
 // previous item's tail.
 //
-//   warpgroup 0 (warps 0-3)    warp 0 producer: TMA loads of K and V tiles (128 keys x d, 128-byte
-//                              swizzle) into a ring; warp 1 MMA issuer: S = Q K^T (A, B from shared
-//                              memory), O_j = P V (A = P from tensor memory) and, for d = 64, the row
-//                              sums P x ones; warps 2-3 idle
-//   warpgroups 1-2 (warps 4-11) softmax, two threads per row: group 1 takes columns 0-63 of the S
-//                              tile, group 2 columns 64-127.  S from tensor memory, causal / window
-//                              mask, the row maximum exchanged through shared memory,
-//                              P = bf16(exp2(..)) back into tensor memory over S.  In decode the 16
-//                              real rows are read with the 16x256b shape, four threads per row.
-//   warpgroup 3 (warps 12-15)   fold: stages the next item's Q tile in shared memory; O_j from tensor
-//                              memory folded into the row's running (M, L, A) in registers (prefill)
-//                              or written out as the tile's partial (decode); the epilogue
+//   warpgroup 0 (warps 0-3)    control.  Warp 0: TMA loads of K and V tiles (128 keys x d, 128-byte
+//                              swizzle) into a ring.  Warp 1: issues S = Q K^T (A, B from shared
+//                              memory) up to three tiles ahead.  Warp 2: issues O_j = P V (A = P from
+//                              tensor memory) and, for d = 64, the row sums of P in the same
+//                              instruction.  Warp 3: copies each item's Q tile into the swizzled
+//                              operand layout, two items ahead.
+//   warpgroups 1-2 (warps 4-11) softmax, thread = row; the groups take alternate tiles.  S from
+//                              tensor memory, causal / window mask, row maximum, then (the two
+//                              groups strictly in turn) P = bf16(exp2(..)) back into tensor memory
+//                              over S.  In decode the 16 real rows are read with the 16x256b shape,
+//                              four threads per row.
+//   warpgroup 3 (warps 12-15)   fold: O_j from tensor memory folded into the row's running (M, L, A)
+//                              in registers (prefill) or written out as the tile's partial
+//                              (decode); the epilogue
 //
-// Registers are moved between the warpgroups with setmaxnreg (48 / 112 / 112 / 232 per thread).
+// Tensor memory: three S / P buffers of 128 columns and one O buffer.  Registers are moved between
+// the warpgroups with setmaxnreg (48 / 152 / 152 / 160 per thread at d = 64, 48 / 112 / 112 / 232
+// at d = 128).
 //
 // The arithmetic is the canonical tile-partial + fold of common.cuh: every key tile yields an
 // independent partial with its own maximum and the partials are folded in ascending tile order
@@ -208,16 +212,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         const uint64_t q_desc0 = smem_desc(smem_u32(q_smem), 16);
         const uint64_t k_desc0 = smem_desc(smem_u32(k_smem), 16);
         TC_LAP_DECL
-        for (TcCursor c = cursor_begin(args); cursor_valid(args, c); cursor_advance(args, c)) {
-            const uint32_t t = c.t;
+        uint32_t t = 0, it = 0;
+        bool ok = true;
+        for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item), ++it) {
+          const int n_tiles = decode_item(args, item).n_tiles;
+          for (int j = 0; j < n_tiles; ++j, ++t) {
             const int slot = int(t % LT::kStages);
-            const int qb = int(c.it & 1);
+            const int qb = int(it & 1);
             const int sb = int(t % LT::kSBufs);
             // The buffer's previous contents, P of tile t - 3, must have been consumed.
             if (t >= LT::kSBufs &&
-                !mbar_wait(&bars->pv_done[sb], (t / LT::kSBufs - 1) & 1, abort_flag, args.status, 12)) break;
-            if (c.j == 0 && !mbar_wait(&bars->q_full[qb], (c.it >> 1) & 1, abort_flag, args.status, 4)) break;
-            if (!mbar_wait(&bars->k_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 3)) break;
+                !mbar_wait(&bars->pv_done[sb], (t / LT::kSBufs - 1) & 1, abort_flag, args.status, 12)) { ok = false; break; }
+            if (j == 0 && !mbar_wait(&bars->q_full[qb], (it >> 1) & 1, abort_flag, args.status, 4)) { ok = false; break; }
+            if (!mbar_wait(&bars->k_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 3)) { ok = false; break; }
             tc_fence_after();
             TC_LAP(0)
             TC_EVT(t, 3)
@@ -237,11 +244,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 TC_LAP(1)
                 tc_commit(&bars->k_empty[slot]);
                 tc_commit(&bars->s_full[sb]);
-                if (c.j + 1 == c.w.n_tiles) tc_commit(&bars->q_empty[qb]);   // the item's Q tile was read for the last time
+                if (j + 1 == n_tiles) tc_commit(&bars->q_empty[qb]);   // the item's Q tile was read for the last time
                 TC_LAP(2)
             }
             __syncwarp();
             TC_EVT(t, 4)
+          }
         }
         if (elect_one()) { TC_LAP_STORE(3) }
     } else if (warp == 2) {
