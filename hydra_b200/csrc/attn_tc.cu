@@ -743,9 +743,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     #pragma unroll
                     for (int u = 0; u < 2; ++u) {
                         #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
+                        for (int i = 0; i < 32; i += 2) {
                             const int col = hb * 64 + u * 32 + i;
-                            A[col] = fold_value(A[col], a, __uint_as_float(o[u][i]), b);
+                            fold_value2(A[col], A[col + 1], a, o[u][i], o[u][i + 1], b);
                         }
                     }
                 }
