@@ -109,55 +109,62 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
             }
         }
     } else if (warp == 1) {
-        // ===== MMA issuer: S(t + 1) is issued before P(t) is awaited, inside an item =====
-        if (lane == 0) {
+        // ===== MMA issuer: S(t + 1) is issued before P(t) is awaited, inside an item.  The whole warp
+        // walks the loop and waits, so control flow stays warp-uniform; one elected lane issues the
+        // tcgen05 instructions (a lane in a divergent branch pays several times more per instruction). =====
+        {
             constexpr uint32_t idesc_qk = instr_desc(kTileKeys, false);
             constexpr uint32_t idesc_pv = instr_desc(kD, true);
-            const uint32_t q_addr = smem_u32(q_smem);
-            const uint32_t k_addr = smem_u32(k_smem);
-            const uint32_t v_addr = smem_u32(v_smem);
+            const uint64_t q_desc0 = smem_desc(smem_u32(q_smem), 16);
+            const uint64_t k_desc0 = smem_desc(smem_u32(k_smem), 16);
+            const uint64_t v_desc0 = smem_desc(smem_u32(v_smem), kTileKeys * 128);
             auto issue_qk = [&](uint32_t t, bool last) -> bool {
                 if (!mbar_wait(&bars->k_full, t & 1, abort_flag, args.status, 3)) return false;
                 tc_fence_after();
-                const uint32_t s_tmem = tmem + (t & 1) * kTileKeys;
-                #pragma unroll
-                for (int b = 0; b < kBlocks256; ++b) {
+                if (elect_one()) {
+                    const uint32_t s_tmem = tmem + (t & 1) * kTileKeys;
                     #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        const uint32_t off = b * (kRows * 128) + ks * 32;
-                        mma_ss(s_tmem, smem_desc(q_addr + off, 16), smem_desc(k_addr + off, 16), idesc_qk,
-                               (b | ks) != 0 ? 1u : 0u);
+                    for (int b = 0; b < kBlocks256; ++b) {
+                        #pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            const uint64_t off = uint64_t((b * (kRows * 128) + ks * 32) >> 4);
+                            mma_ss(s_tmem, q_desc0 + off, k_desc0 + off, idesc_qk, (b | ks) != 0 ? 1u : 0u);
+                        }
                     }
+                    tc_commit(&bars->k_empty);
+                    tc_commit(&bars->s_full[t & 1]);
+                    if (last) tc_commit(&bars->q_empty);
                 }
-                tc_commit(&bars->k_empty);
-                tc_commit(&bars->s_full[t & 1]);
-                if (last) tc_commit(&bars->q_empty);
+                __syncwarp();
                 return true;
             };
             uint32_t t = 0, it = 0;
             bool ok = true;
             for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item), ++it) {
-                const TcItem w = decode_item(args, item);
+                const int n_tiles = decode_item(args, item).n_tiles;
                 if (!mbar_wait(&bars->q_full, it & 1, abort_flag, args.status, 4)) break;
                 tc_fence_after();
-                ok = issue_qk(t, w.n_tiles == 1);
-                for (int j = 0; ok && j < w.n_tiles; ++j, ++t) {
-                    if (j + 1 < w.n_tiles) {
-                        ok = issue_qk(t + 1, j + 2 == w.n_tiles);
+                ok = issue_qk(t, n_tiles == 1);
+                for (int j = 0; ok && j < n_tiles; ++j, ++t) {
+                    if (j + 1 < n_tiles) {
+                        ok = issue_qk(t + 1, j + 2 == n_tiles);
                         if (!ok) break;
                     }
                     if (!mbar_wait(&bars->p_full[t & 1], (t >> 1) & 1, abort_flag, args.status, 5)) { ok = false; break; }
                     if (!mbar_wait(&bars->v_full, t & 1, abort_flag, args.status, 6)) { ok = false; break; }
                     if (t > 0 && !mbar_wait(&bars->o_free, (t - 1) & 1, abort_flag, args.status, 7)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t p_tmem = tmem + (t & 1) * kTileKeys;
-                    #pragma unroll
-                    for (int ks = 0; ks < kTileKeys / 16; ++ks) {
-                        mma_ts(tmem + kOCol256, p_tmem + ks * 8, smem_desc(v_addr + ks * 2048, kTileKeys * 128), idesc_pv,
-                               ks != 0 ? 1u : 0u);
+                    if (elect_one()) {
+                        const uint32_t p_tmem = tmem + (t & 1) * kTileKeys;
+                        #pragma unroll
+                        for (int ks = 0; ks < kTileKeys / 16; ++ks) {
+                            mma_ts(tmem + kOCol256, p_tmem + ks * 8, v_desc0 + uint64_t((ks * 2048) >> 4), idesc_pv,
+                                   ks != 0 ? 1u : 0u);
+                        }
+                        tc_commit(&bars->v_empty);
+                        tc_commit(&bars->o_full);
                     }
-                    tc_commit(&bars->v_empty);
-                    tc_commit(&bars->o_full);
+                    __syncwarp();
                 }
             }
         }
@@ -366,8 +373,8 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
                         }
                     } else {
                         #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            A[chunk * 32 + i] = fold_value(A[chunk * 32 + i], a, __uint_as_float(o[i]), b);
+                        for (int i = 0; i < 32; i += 2) {
+                            fold_value2(A[chunk * 32 + i], A[chunk * 32 + i + 1], a, o[i], o[i + 1], b);
                         }
                     }
                 }
