@@ -278,6 +278,8 @@ merge_tiles_kernel(const AttnShape shape, const BatchMeta meta, const float* __r
     __shared__ float coef_b[kMergeChunk];
     __shared__ float part_l[kMergeChunk];
     __shared__ float warp_max[4];
+    pdl_launch_dependents();
+    pdl_wait();
     const int head = blockIdx.x;
     const int b = blockIdx.y;
     const int d = shape.head_dim;
@@ -537,9 +539,11 @@ hc_status launch_merge(hc_context* ctx, const AttnShape& shape, const BatchMeta&
                        const Workspace& ws, int part_tiles, int world, int rank, const EpilogueArgs& ep,
                        cudaStream_t stream) {
     dim3 mgrid(shape.q_heads, n_seq);
-    merge_tiles_kernel<<<mgrid, kThreads, 0, stream>>>(shape, meta, ws.part_o, ws.part_ml, part_tiles,
-                                                      world, rank, ep);
+    const cudaError_t launched = launch_pdl(merge_tiles_kernel, mgrid, dim3(kThreads), 0, stream, shape, meta,
+                                            static_cast<const float*>(ws.part_o), static_cast<const float*>(ws.part_ml),
+                                            part_tiles, world, rank, ep);
     ctx->launches += 1;
+    if (launched != cudaSuccess) return check_cuda(launched, "merge_tiles_kernel launch");
     return check_cuda(cudaGetLastError(), "merge_tiles_kernel launch");
 }
 

@@ -127,6 +127,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     const int world = max(args.map.world, 1);
     volatile int* abort_flag = &bars->abort_flag;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         TC_TRACE(0);
         for (int i = 0; i < 2; ++i) {
@@ -164,6 +165,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
+    // Everything above touched only this CTA's shared and tensor memory; from here on the kernel
+    // reads what earlier kernels of the stream wrote (prepared q, the cache) and writes its outputs.
+    pdl_wait();
     if (threadIdx.x == 0) TC_TRACE(1);
 
     // Registers follow the work (setmaxnreg, first thing in each warpgroup's branch): the fold
@@ -885,9 +889,11 @@ static hc_status launch_tc(hc_context* ctx, const TcArgs& args, const hc_layer_s
     }
     // Persistent: one CTA per SM at most, each walking items blockIdx.x, blockIdx.x + gridDim.x, ...
     const int grid = std::max(1, std::min(args.n_items, std::max(ctx->sm_count, 1)));
-    attention_tc_kernel<D><<<grid, kTcThreads, smem, stream>>>(*static_cast<const CUtensorMap*>(layer.tmap_k),
-                                                              *static_cast<const CUtensorMap*>(layer.tmap_v), args);
+    const cudaError_t launched = launch_pdl(attention_tc_kernel<D>, grid, kTcThreads, size_t(smem), stream,
+                                            *static_cast<const CUtensorMap*>(layer.tmap_k),
+                                            *static_cast<const CUtensorMap*>(layer.tmap_v), args);
     ctx->launches += 1;
+    if (launched != cudaSuccess) return check_cuda(launched, "attention_tc_kernel launch");
     return check_cuda(cudaGetLastError(), "attention_tc_kernel launch");
 }
 

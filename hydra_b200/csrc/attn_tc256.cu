@@ -57,6 +57,7 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     const int world = max(args.map.world, 1);
     volatile int* abort_flag = &bars->abort_flag;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         mbar_init(&bars->q_full, 128);
         mbar_init(&bars->q_empty, 1);
@@ -82,6 +83,7 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
+    pdl_wait();        // set-up done; from here on the kernel reads what earlier kernels wrote
 
     if (wg == 0) {
     reg_dealloc<48>();
@@ -449,9 +451,11 @@ hc_status launch_tc256(hc_context* ctx, const void* tmap_k, const void* tmap_v, 
         configured[ctx->device & 63] = true;
     }
     const int grid = std::max(1, std::min(n_items, std::max(ctx->sm_count, 1)));
-    attention_tc256_kernel<<<grid, kTcThreads, smem, stream>>>(*static_cast<const CUtensorMap*>(tmap_k),
-                                                              *static_cast<const CUtensorMap*>(tmap_v), args);
+    const cudaError_t launched = launch_pdl(attention_tc256_kernel, grid, kTcThreads, size_t(smem), stream,
+                                            *static_cast<const CUtensorMap*>(tmap_k),
+                                            *static_cast<const CUtensorMap*>(tmap_v), args);
     ctx->launches += 1;
+    if (launched != cudaSuccess) return check_cuda(launched, "attention_tc256_kernel launch");
     return check_cuda(cudaGetLastError(), "attention_tc256_kernel launch");
 }
 

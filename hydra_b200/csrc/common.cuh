@@ -40,6 +40,14 @@ constexpr uint16_t kNoSinkBits = 0xF14A;  // bf16 nearest to -1e30 (-1.00026e30)
 // Seed of a fold that must not count the sink (ranks > 0 of a sequence-sharded cache).
 constexpr float kEmptyMax = -1.0e30f;
 
+// Programmatic dependent launch.  The hot kernels are launched with the stream-serialisation
+// attribute relaxed, so a kernel's blocks may be scheduled (and run their set-up) while the kernel
+// before it in the stream is still finishing.  Each of them lets its successor go at its very top
+// and waits for its predecessors (all of them: the wait is for full completion, memory included)
+// before it touches global memory.  Launched the ordinary way the two instructions do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -59,6 +59,8 @@ prepare_heads_vec_kernel(const PrepArgs args, int total_heads) {
     constexpr int d = 8 * LPV;
     constexpr int half = 4 * LPV;
     constexpr int kPerWarp = 32 / LPV;
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int sub = lane / LPV;
@@ -158,6 +160,8 @@ prepare_heads_vec_kernel(const PrepArgs args, int total_heads) {
 __global__ void __launch_bounds__(kPrepWarps * 32)
 prepare_heads_kernel(const PrepArgs args) {
     __shared__ float stage[kPrepWarps][kMaxHeadDim];
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int d = args.head_dim;
@@ -283,13 +287,13 @@ hc_status launch_prepare(hc_context* ctx, const PrepArgs& args, cudaStream_t str
         const int per_warp = 256 / d;
         const long long groups = (vectors + per_warp - 1) / per_warp;
         const int grid = int(std::min<long long>((groups + kPrepWarps - 1) / kPrepWarps, cap));
-        if (d == 64) prepare_heads_vec_kernel<8><<<grid, kPrepWarps * 32, 0, stream>>>(args, total_heads);
-        else if (d == 128) prepare_heads_vec_kernel<16><<<grid, kPrepWarps * 32, 0, stream>>>(args, total_heads);
-        else prepare_heads_vec_kernel<32><<<grid, kPrepWarps * 32, 0, stream>>>(args, total_heads);
+        if (d == 64) launch_pdl(prepare_heads_vec_kernel<8>, grid, kPrepWarps * 32, 0, stream, args, total_heads);
+        else if (d == 128) launch_pdl(prepare_heads_vec_kernel<16>, grid, kPrepWarps * 32, 0, stream, args, total_heads);
+        else launch_pdl(prepare_heads_vec_kernel<32>, grid, kPrepWarps * 32, 0, stream, args, total_heads);
     } else {
         const long long wanted = (vectors + kPrepWarps - 1) / kPrepWarps;
         const int grid = int(std::min<long long>(wanted, cap));
-        prepare_heads_kernel<<<grid, kPrepWarps * 32, 0, stream>>>(args);
+        launch_pdl(prepare_heads_kernel, grid, kPrepWarps * 32, 0, stream, args);
     }
     ctx->launches += 1;
     return check_cuda(cudaGetLastError(), "prepare_heads_kernel launch");
