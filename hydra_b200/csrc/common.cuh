@@ -86,9 +86,10 @@ __device__ __forceinline__ float fold_value(float acc, float a, float part, floa
 __device__ __forceinline__ float sigmoid_gate(float g) {
     return __fdiv_rn(1.0f, __fadd_rn(1.0f, ex2(__fmul_rn(-g, kLog2e))));
 }
-// The last step of a row: divide by the denominator, then the optional gate.
+// The last step of a row: the correctly rounded reciprocal of the denominator (one per row; the
+// compiler shares it between the row's elements) times the numerator, then the optional gate.
 __device__ __forceinline__ float finish_value(float A, float L, bool gated, float g) {
-    float out = __fdiv_rn(A, L);
+    float out = __fmul_rn(A, __frcp_rn(L));
     if (gated) out = __fmul_rn(out, sigmoid_gate(g));
     return out;
 }
