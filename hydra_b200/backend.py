@@ -399,6 +399,14 @@ class AttentionBackend:
         _check(self._lib.hc_qwen_apply_output_gate(self.ctx.handle, _ptr(output), _ptr(gate), count,
                                                    io_dtype, _stream(stream)))
 
+    # One layer's step with device buffers: append + attention (prefill if tokens > 1, else decode);
+    # the per-layer order of the reference's encoders as one call, one prologue launch for q, k, v.
+    def layer_step(self, cache: KVCache, layer: int, q, k, v, out, tokens: int, first_position: int,
+                   params: AttnParams, seq: int = 0, stream=None) -> None:
+        s = params.struct()
+        _check(self._lib.hc_layer_step(self.ctx.handle, cache.handle, layer, seq, _ptr(q), _ptr(k), _ptr(v),
+                                       _ptr(out), tokens, first_position, ctypes.byref(s), _stream(stream)))
+
     # One whole step with host buffers (numpy arrays or raw addresses).
     def layer_step_host(self, cache: KVCache, layer: int, q, k, v, out, tokens: int,
                         first_position: int, params: AttnParams, seq: int = 0, stream=None) -> None:

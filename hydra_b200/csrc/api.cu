@@ -173,9 +173,12 @@ bool use_tensor_path(const hc_attn_params* p, const AttnShape& shape, hc_status*
 }
 
 // The body shared by hc_attention_prefill and hc_attention_prefill_partial.
+// With k_fused / v_fused set (hc_layer_step; one pass, tokens <= the prologue workspace) the K/V
+// append of the same tokens rides in the Q prologue's launch.
 hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q,
                        void* out, int tokens, int first_position, const hc_attn_params* p,
-                       bool partial_mode, cudaStream_t stream) {
+                       bool partial_mode, cudaStream_t stream, const void* k_fused = nullptr,
+                       const void* v_fused = nullptr) {
     if (!ctx || !q || !out) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
     hc_status st = validate_params(cache, layer, p);
     if (st != HC_OK) return st;
@@ -198,11 +201,16 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
         const int count = std::min(step, tokens - start);
         const unsigned char* q_rows = offset_rows(q, size_t(start), size_t(p->q_heads) * d * mult, p->io_dtype);
         const uint16_t* q_bf16 = reinterpret_cast<const uint16_t*>(q_rows);
-        if (prep) {
+        if (prep || k_fused) {
             PrepArgs args{};
             fill_common(args, p);
-            fill_q_job(args.job[0], p, q_rows, cache->ws.qprep);
-            args.n_jobs = 1;
+            int jobs = 0;
+            if (prep) fill_q_job(args.job[jobs++], p, q_rows, cache->ws.qprep);
+            if (k_fused) {
+                fill_kv_jobs(args, jobs, p, k_fused, v_fused);
+                jobs += 2;
+            }
+            args.n_jobs = jobs;
             args.tokens = count;
             args.first_position = first_position + start;
             args.batched = 0;
@@ -210,7 +218,7 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
             args.cache = view;
             st = launch_prepare(ctx, args, stream);
             if (st != HC_OK) return st;
-            q_bf16 = cache->ws.qprep;
+            if (prep) q_bf16 = cache->ws.qprep;
         }
         EpilogueArgs ep{};
         ep.io_dtype = p->io_dtype;
@@ -954,6 +962,27 @@ hc_status hc_qwen_apply_output_gate(hc_context* ctx, void* output, const void* g
     return launch_output_gate(ctx, output, gate, count, io_dtype, static_cast<cudaStream_t>(stream));
 }
 
+hc_status hc_layer_step(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q, const void* k,
+                        const void* v, void* out, int tokens, int first_position,
+                        const hc_attn_params* params, void* stream) {
+    if (!ctx || !q || !k || !v || !out) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    hc_status st = validate_params(cache, layer, params);
+    if (st != HC_OK) return st;
+    if (tokens <= 0) return fail(HC_INVALID_ARGUMENT, "tokens must be positive");
+    if (tokens > 1 && tokens <= cache->ws.qprep_tokens) {
+        // One prologue launch for k, v and q, then the attention kernel.
+        return prefill_impl(ctx, cache, layer, seq, q, out, tokens, first_position, params, false,
+                            static_cast<cudaStream_t>(stream), k, v);
+    }
+    st = hc_kv_append(ctx, cache, layer, seq, k, v, tokens, first_position, params, stream);
+    if (st != HC_OK) return st;
+    if (tokens == 1) {
+        const int position = first_position;
+        return hc_attention_decode(ctx, cache, layer, &seq, &position, 1, q, out, params, stream);
+    }
+    return hc_attention_prefill(ctx, cache, layer, seq, q, out, tokens, first_position, params, stream);
+}
+
 hc_status hc_layer_step_host(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q, const void* k,
                              const void* v, void* out, int tokens, int first_position,
                              const hc_attn_params* params, void* stream) {
@@ -987,14 +1016,7 @@ hc_status hc_layer_step_host(hc_context* ctx, hc_kv_cache* cache, int layer, int
     if (err != cudaSuccess) return check_cuda(err, "host to device copy");
     hc_attn_params local = *params;
     if (sep_gate) local.gate = dg;
-    st = hc_kv_append(ctx, cache, layer, seq, dk, dv, tokens, first_position, &local, stream);
-    if (st != HC_OK) return st;
-    if (tokens == 1) {
-        const int position = first_position;
-        st = hc_attention_decode(ctx, cache, layer, &seq, &position, 1, dq, dout, &local, stream);
-    } else {
-        st = hc_attention_prefill(ctx, cache, layer, seq, dq, dout, tokens, first_position, &local, stream);
-    }
+    st = hc_layer_step(ctx, cache, layer, seq, dq, dk, dv, dout, tokens, first_position, &local, stream);
     if (st != HC_OK) return st;
     err = cudaMemcpyAsync(out, dout, o_bytes, cudaMemcpyDeviceToHost, s);
     if (err == cudaSuccess) err = cudaStreamSynchronize(s);

@@ -240,15 +240,20 @@ class PathRunner:
             torch.cuda.synchronize()
 
     # -- the passes ---------------------------------------------------------------------------------
-    def prefill_pass(self, stream=None, layers=None):
-        """Append + attend for every chunk of the prompt, every layer."""
+    def prefill_pass(self, stream=None, layers=None, fused=False):
+        """Append + attend for every chunk of the prompt, every layer: two calls per chunk
+        (hc_kv_append, hc_attention_prefill) or, with `fused`, one (hc_layer_step)."""
         cfg = self.cfg
         for layer in (range(len(cfg.layers)) if layers is None else layers):
             t, params = self.dev[layer], self.params[layer]
             for start in range(0, cfg.prompt, cfg.chunk):
                 n = min(cfg.chunk, cfg.prompt - start)
-                self.backend.write_key_value(self.cache, layer, t["k"][start:], t["v"][start:], n, start, params, stream=stream)
-                self.backend.attention_prefill(self.cache, layer, t["q"][start:], t["out"][start:], n, start, params, stream=stream)
+                if fused:
+                    self.backend.layer_step(self.cache, layer, t["q"][start:], t["k"][start:], t["v"][start:],
+                                            t["out"][start:], n, start, params, stream=stream)
+                else:
+                    self.backend.write_key_value(self.cache, layer, t["k"][start:], t["v"][start:], n, start, params, stream=stream)
+                    self.backend.attention_prefill(self.cache, layer, t["q"][start:], t["out"][start:], n, start, params, stream=stream)
 
     def decode_step(self, row: int, position: int, stream=None, layers=None, append=True):
         """One token (batch 1): its K/V appended at `position`, then attention, every layer."""

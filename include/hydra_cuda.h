@@ -336,6 +336,19 @@ HC_API hc_status hc_qwen_split_query_gate(hc_context* ctx, const void* combined,
 HC_API hc_status hc_qwen_apply_output_gate(hc_context* ctx, void* output, const void* gate,
                                            size_t count, int io_dtype, void* stream);
 
+/* ---- one layer's step ------------------------------------------------------------------------- */
+
+/* Append + attend for `tokens` tokens of one sequence in one call, DEVICE buffers: the per-layer
+ * order of the reference's encoders (norm -> RoPE -> cache write -> attention -> gate:
+ * Sources/HydraMetal/ForwardEncoder.swift attention block; Sources/HydraReference/
+ * Gemma4ReferenceLayer.swift:154-157, 234-246) as one entry point.  Results are bit for bit those
+ * of hc_kv_append followed by hc_attention_prefill (tokens > 1) or hc_attention_decode
+ * (tokens == 1); for a chunk that fits the prologue workspace the K/V append and the query prologue
+ * share one launch.  It does not move the sequence length. */
+HC_API hc_status hc_layer_step(hc_context* ctx, hc_kv_cache* cache, int layer, int seq,
+                               const void* q, const void* k, const void* v, void* out, int tokens,
+                               int first_position, const hc_attn_params* params, void* stream);
+
 /* ---- host-buffer convenience (what a runner without device buffers of its own calls) --------- */
 
 /* One whole step of the path with HOST buffers: copies q, k, v (and gate) to the device, appends,

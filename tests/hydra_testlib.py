@@ -115,6 +115,15 @@ class Layer:
         self.ctx.check()
         return to_host(out)
 
+    def step(self, q, k, v, first_position, seq=0):
+        """hc_layer_step: append + attention of the same tokens in one call."""
+        tokens = q.shape[0]
+        qd, kd, vd = to_device(q, self.io), to_device(k, self.io), to_device(v, self.io)
+        out = device_empty((tokens, self.q_heads, self.d), self.io)
+        self.backend.layer_step(self.cache, 0, qd, kd, vd, out, tokens, first_position, self.params, seq=seq)
+        self.ctx.check()
+        return to_host(out)
+
     def decode(self, q, positions, gate=None, seq_ids=None):
         n = q.shape[0]
         qd = to_device(q, self.io)

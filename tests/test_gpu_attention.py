@@ -438,6 +438,37 @@ def test_layer_step_with_host_buffers(hb, ctx):
     layer.close()
 
 
+@pytest.mark.parametrize("d,window", [(64, 0), (128, 96), (256, 0), (96, 0)])
+def test_layer_step_equals_append_then_attention(hb, ctx, d, window):
+    """hc_layer_step (one prologue launch for k, v and q) gives bit for bit what hc_kv_append followed
+    by hc_attention_prefill / hc_attention_decode gives, with norm and rotation in the prologue."""
+    rng = np.random.default_rng(152 + d)
+    qh, kvh, tokens = 16, 4, 300
+    q = tl.normal_bf16(rng, (tokens + 1, qh, d))
+    k = tl.normal_bf16(rng, (tokens + 1, kvh, d))
+    v = tl.normal_bf16(rng, (tokens + 1, kvh, d))
+    sinks = tl.normal_bf16(rng, (qh,))
+    qw, kw = tl.normal_bf16(rng, (d,)), tl.normal_bf16(rng, (d,))
+    inv = ho.inverse_frequencies(d, 10000.0, d // 2)
+    outs = []
+    for fused in (False, True):
+        layer = tl.Layer(hb, ctx, qh, kvh, d, 512, window=window, sinks=sinks, rope_inv_freq=inv, q_norm=qw, k_norm=kw)
+        if fused:
+            first = layer.step(q[:200], k[:200], v[:200], 0)
+            second = layer.step(q[200:tokens], k[200:tokens], v[200:tokens], 200)
+            last = layer.step(q[tokens:], k[tokens:], v[tokens:], tokens)
+        else:
+            layer.append(k[:200], v[:200], 0)
+            first = layer.prefill(q[:200], 0)
+            layer.append(k[200:tokens], v[200:tokens], 200)
+            second = layer.prefill(q[200:tokens], 200)
+            layer.append(k[tokens:], v[tokens:], tokens)
+            last = layer.decode(q[tokens:], [tokens])
+        outs.append(np.concatenate([first, second, last]))
+        layer.close()
+    assert np.array_equal(outs[0], outs[1])
+
+
 # ---- the tcgen05 path -------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("case", [
