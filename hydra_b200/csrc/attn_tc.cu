@@ -306,32 +306,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const int qb = int(it & 1);
             // The buffer was last read by item it - 2.
             if (it >= 2 && !mbar_wait(&bars->q_empty[qb], ((it >> 1) - 1) & 1, abort_flag, args.status, 10)) break;
-            unsigned char* dst = q_smem + qb * LT::kQBytes;
+            // All of the tile's 16-byte pieces are put in flight at once (cp.async, no registers), so
+            // an item costs one round trip to global memory rather than one per row.
+            const uint32_t dst = smem_u32(q_smem + qb * LT::kQBytes);
             #pragma unroll 1
             for (int r = 0; r < 4; ++r) {
                 const int row = r * 32 + lane;
                 const int t_local = row >> args.log_group;
                 const int g = row & (G - 1);
                 const bool valid = t_local < w.valid_tokens;
-                const uint16_t* src = args.q + (size_t(w.row0 + t_local) * args.q_heads + size_t(w.kv_head) * G + g) * D;
+                const uint16_t* src = valid
+                    ? args.q + (size_t(w.row0 + t_local) * args.q_heads + size_t(w.kv_head) * G + g) * D
+                    : args.q;
                 #pragma unroll
                 for (int b = 0; b < LT::kBlocks; ++b) {
                     #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        uint4 value[4];
-                        #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            value[u] = make_uint4(0, 0, 0, 0);
-                            if (valid) value[u] = *reinterpret_cast<const uint4*>(src + b * 64 + (half * 4 + u) * 8);
-                        }
-                        #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const int ch = half * 4 + u;
-                            *reinterpret_cast<uint4*>(dst + b * (kRows * 128) + row * 128 + ((ch ^ (row & 7)) << 4)) = value[u];
-                        }
+                    for (int ch = 0; ch < 8; ++ch) {
+                        cp_async16(dst + b * (kRows * 128) + row * 128 + ((ch ^ (row & 7)) << 4), src + b * 64 + ch * 8,
+                                   valid ? 16u : 0u);
                     }
                 }
             }
+            cp_async_wait_all();
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->q_full[qb]);
