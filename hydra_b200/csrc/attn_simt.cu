@@ -268,8 +268,12 @@ decode_tiles_kernel(const AttnShape shape, const CacheView cache, const BatchMet
 // ---- merge: the fold over a row's tile partials ------------------------------------------------
 // The running maximum is a prefix maximum (exact under any association), so the coefficients of
 // every step are computed in parallel and only `acc = fma(acc, a, part * b)` stays sequential.
-constexpr int kMergeChunk = 1024;            // tiles folded per pass
+constexpr int kMergeChunk = 1024;            // tiles folded per pass, at most (8 per thread)
 
+// COLS = columns of the row per thread: the block has min(128, head_dim) threads (64 for
+// head_dim <= 64), so no thread idles, and the fewer columns a thread carries the further ahead of
+// its dependent chain it fetches the partials (256 / 8 / COLS ... tiles in flight).
+template <int COLS>
 __global__ void __launch_bounds__(kThreads)
 merge_tiles_kernel(const AttnShape shape, const BatchMeta meta, const float* __restrict__ part_o,
                    const float* __restrict__ part_ml, int part_tiles, int world, int rank,
@@ -278,6 +282,9 @@ merge_tiles_kernel(const AttnShape shape, const BatchMeta meta, const float* __r
     __shared__ float coef_b[kMergeChunk];
     __shared__ float part_l[kMergeChunk];
     __shared__ float warp_max[4];
+    const int threads = blockDim.x;              // 64 or 128
+    const int warps = threads >> 5;
+    const int chunk_tiles = threads * 8;
     pdl_launch_dependents();
     pdl_wait();
     const int head = blockIdx.x;
@@ -305,11 +312,13 @@ merge_tiles_kernel(const AttnShape shape, const BatchMeta meta, const float* __r
         M = kEmptyMax;
         L = 0.0f;
     }
-    constexpr int kCols = 4;                 // head_dim <= 512 = 4 * 128 threads
-    float A[kCols] = {0.0f, 0.0f, 0.0f, 0.0f};
+    constexpr int kCols = COLS;
+    float A[kCols];
+    #pragma unroll
+    for (int cidx = 0; cidx < kCols; ++cidx) A[cidx] = 0.0f;
 
-    for (int base = 0; base < n_tiles; base += kMergeChunk) {
-        const int count = min(kMergeChunk, n_tiles - base);
+    for (int base = 0; base < n_tiles; base += chunk_tiles) {
+        const int count = min(chunk_tiles, n_tiles - base);
         __syncthreads();
         // Thread t owns 8 consecutive tiles: local inclusive prefix maximum, then a block scan.
         float local[8];
@@ -347,20 +356,20 @@ merge_tiles_kernel(const AttnShape shape, const BatchMeta meta, const float* __r
             }
         }
         float chunk_max = M;
-        for (int w = 0; w < 4; ++w) chunk_max = fmaxf(chunk_max, warp_max[w]);
+        for (int w = 0; w < warps; ++w) chunk_max = fmaxf(chunk_max, warp_max[w]);
         __syncthreads();
 
         // The sequential part.  Every thread carries L (same chain, same bits) and its columns.
         const float* o_base = part_o + (row * part_tiles + base) * d;
-        // The partials are fetched eight tiles ahead of the dependent chain that consumes them.
-        constexpr int kAhead = 8;
+        // The partials are fetched well ahead of the dependent chain that consumes them.
+        constexpr int kAhead = 32 / COLS;
         for (int t0 = 0; t0 < count; t0 += kAhead) {
             float part[kAhead][kCols];
             #pragma unroll
             for (int u = 0; u < kAhead; ++u) {
                 #pragma unroll
                 for (int cidx = 0; cidx < kCols; ++cidx) {
-                    const int i = tid + cidx * kThreads;
+                    const int i = tid + cidx * threads;
                     part[u][cidx] = (t0 + u < count && i < d) ? __ldg(o_base + size_t(t0 + u) * d + i) : 0.0f;
                 }
             }
@@ -381,7 +390,7 @@ merge_tiles_kernel(const AttnShape shape, const BatchMeta meta, const float* __r
 
     #pragma unroll
     for (int cidx = 0; cidx < kCols; ++cidx) {
-        const int i = tid + cidx * kThreads;
+        const int i = tid + cidx * threads;
         if (i < d) write_result(ep, size_t(b), shape.q_heads, head, d, i, A[cidx], M, L);
     }
 }
@@ -539,7 +548,11 @@ hc_status launch_merge(hc_context* ctx, const AttnShape& shape, const BatchMeta&
                        const Workspace& ws, int part_tiles, int world, int rank, const EpilogueArgs& ep,
                        cudaStream_t stream) {
     dim3 mgrid(shape.q_heads, n_seq);
-    const cudaError_t launched = launch_pdl(merge_tiles_kernel, mgrid, dim3(kThreads), 0, stream, shape, meta,
+    const int d = shape.head_dim;
+    const int threads = d <= 64 ? 64 : kThreads;
+    const int cols = (d + threads - 1) / threads;
+    auto kernel = cols <= 1 ? merge_tiles_kernel<1> : cols == 2 ? merge_tiles_kernel<2> : merge_tiles_kernel<4>;
+    const cudaError_t launched = launch_pdl(kernel, mgrid, dim3(threads), 0, stream, shape, meta,
                                             static_cast<const float*>(ws.part_o), static_cast<const float*>(ws.part_ml),
                                             part_tiles, world, rank, ep);
     ctx->launches += 1;

@@ -294,15 +294,18 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         auto stage_q = [&](const TcItem& w) {
             const bool valid = t_local < w.valid_tokens;
             const uint16_t* src = args.q + (size_t(w.row0 + t_local) * args.q_heads + size_t(w.kv_head) * G + g) * kD;
+            // The row's 32 pieces of 16 bytes go global -> shared in one flight (cp.async, no registers).
+            const uint32_t dst = smem_u32(q_smem);
+            const uint16_t* from = valid ? src : args.q;
             #pragma unroll
             for (int b = 0; b < kBlocks256; ++b) {
                 #pragma unroll
                 for (int ch = 0; ch < 8; ++ch) {
-                    uint4 value = make_uint4(0, 0, 0, 0);
-                    if (valid) value = *reinterpret_cast<const uint4*>(src + b * 64 + ch * 8);
-                    *reinterpret_cast<uint4*>(q_smem + b * (kRows * 128) + row * 128 + ((ch ^ (row & 7)) << 4)) = value;
+                    cp_async16(dst + b * (kRows * 128) + row * 128 + ((ch ^ (row & 7)) << 4), from + b * 64 + ch * 8,
+                               valid ? 16u : 0u);
                 }
             }
+            cp_async_wait_all();
             fence_proxy_async();
             mbar_arrive(&bars->q_full);
         };
