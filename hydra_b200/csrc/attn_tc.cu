@@ -179,8 +179,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         if (lane == 0) {
             uint32_t t = 0;
             bool ok = true;
-            for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item)) {
-                const TcItem w = decode_item(args, item);
+            for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk)) {
+                const TcItem& w = walk.w;
                 const int plane = w.seq * args.kv_heads + w.kv_head;
                 for (int j = 0; j < w.n_tiles; ++j, ++t) {
                     const int slot = int(t % LT::kStages);
@@ -204,7 +204,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         tma_load_3d(v_smem + slot * LT::kTileBytes + b * (kTileKeys * 128), &tmap_v,
                                     &bars->v_full[slot], b * 64, row0, plane);
                     }
-                    TC_TRACE(2);
                 }
             }
         }
@@ -218,8 +217,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         TC_LAP_DECL
         uint32_t t = 0, it = 0;
         bool ok = true;
-        for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item), ++it) {
-          const int n_tiles = decode_item(args, item).n_tiles;
+        for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk), ++it) {
+          const int n_tiles = walk.w.n_tiles;
           for (int j = 0; j < n_tiles; ++j, ++t) {
             const int slot = int(t % LT::kStages);
             const int qb = int(it & 1);
@@ -267,8 +266,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         const uint32_t v_base = smem_u32(v_smem);
         uint32_t t = 0;
         bool ok = true;
-        for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item)) {
-            const int n_tiles = decode_item(args, item).n_tiles;
+        for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk)) {
+            const int n_tiles = walk.w.n_tiles;
             for (int j = 0; j < n_tiles; ++j, ++t) {
                 const int slot = int(t % LT::kStages);
                 const int sb = int(t % LT::kSBufs);
@@ -301,8 +300,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         // K-major layout, up to two items ahead of the S issuer, so the global-memory latency of a
         // new item never sits in another role's path.  Lane l copies rows l, l + 32, l + 64, l + 96. =====
         uint32_t it = 0;
-        for (int item = first_item(args); item < args.n_items; item = next_item(args, item), ++it) {
-            const TcItem w = decode_item(args, item);
+        for (TcItemIter walk = items_begin(args); walk.item < args.n_items; items_next(args, walk), ++it) {
+            const TcItem& w = walk.w;
             const int qb = int(it & 1);
             // The buffer was last read by item it - 2.
             if (it >= 2 && !mbar_wait(&bars->q_empty[qb], ((it >> 1) - 1) & 1, abort_flag, args.status, 10)) break;
@@ -348,8 +347,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         uint32_t t = 0;
         bool ok = true;
         TC_LAP_DECL
-        for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item)) {
-            const TcItem w = decode_item(args, item);
+        for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk)) {
+            const TcItem& w = walk.w;
             const bool valid = t_local < w.valid_tokens;
             const bool warp_has_rows = quad * 32 < (w.valid_tokens << args.log_group);   // warp-uniform
             const int pos = valid ? w.first_pos + t_local : -1;
@@ -656,23 +655,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         };
         uint32_t t = 0, it = 0;
         bool ok = true;
-        int item = first_item(args);
+        TcItemIter walk = items_begin(args);
         TC_LAP_DECL
-        while (ok && item < args.n_items) {
-            const TcItem w = decode_item(args, item);
-            const int nxt = next_item(args, item);
+        // The head's sink is fetched one item ahead (prefill only: decode writes raw partials and the
+        // merge kernel seeds the fold), so its latency never sits at an item's start.
+        const bool wants_sink = args.count_sink && args.sinks != nullptr && !args.decode;
+        uint16_t sink_bits = kNoSinkBits;
+        if (wants_sink && walk.item < args.n_items) sink_bits = args.sinks[walk.w.kv_head * G + g];
+        while (ok && walk.item < args.n_items) {
+            const TcItem w = walk.w;
+            items_next(args, walk);
             const int head = w.kv_head * G + g;
             const bool valid = t_local < w.valid_tokens;
             const bool warp_has_rows = quad * 32 < (w.valid_tokens << args.log_group);   // warp-uniform
             float M, L;
             if (args.count_sink) {
-                const uint16_t bits = args.sinks ? args.sinks[head] : kNoSinkBits;
-                M = __fmul_rn(bf16_bits_to_float(bits), kLog2e);
+                M = __fmul_rn(bf16_bits_to_float(sink_bits), kLog2e);
                 L = 1.0f;
             } else {
                 M = kEmptyMax;
                 L = 0.0f;
             }
+            if (wants_sink && walk.item < args.n_items) sink_bits = args.sinks[walk.w.kv_head * G + g];
             float A[D];
             #pragma unroll
             for (int i = 0; i < D; ++i) A[i] = 0.0f;
@@ -680,7 +684,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 TC_LAP(5)
                 if (!mbar_wait(&bars->o_full, t & 1, abort_flag, args.status, 9)) { ok = false; break; }
                 TC_LAP(0)
-                if (threadIdx.x == 384) TC_TRACE(7);
                 if (threadIdx.x == 384) TC_EVT(t, 10)
                 tc_fence_after();
                 if (!warp_has_rows) {
@@ -791,8 +794,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     }
                 }
             }
-            if (threadIdx.x == 384) TC_TRACE(8);
-            item = nxt;
             ++it;
             TC_LAP(3)
         }

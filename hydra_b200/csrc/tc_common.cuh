@@ -126,6 +126,31 @@ __device__ __forceinline__ void cursor_advance(const TcArgs& args, TcCursor& c) 
     }
 }
 
+// The walk over a CTA's items: each item is decoded once per role (its decoding costs a few integer
+// divisions, which a role pays on its critical path at every item boundary).
+struct TcItemIter {
+    int item;          // index in the work list, or n_items at the end
+    TcItem w;
+};
+__device__ __forceinline__ void items_seek(const TcArgs& args, TcItemIter& it) {
+    for (; it.item < args.n_items; it.item += gridDim.x) {
+        it.w = decode_item(args, it.item);
+        if (it.w.n_tiles > 0) return;
+    }
+    it.item = args.n_items;
+}
+__device__ __forceinline__ TcItemIter items_begin(const TcArgs& args) {
+    TcItemIter it;
+    it.item = blockIdx.x;
+    it.w = TcItem{};
+    items_seek(args, it);
+    return it;
+}
+__device__ __forceinline__ void items_next(const TcArgs& args, TcItemIter& it) {
+    it.item += gridDim.x;
+    items_seek(args, it);
+}
+
 // bf16x2 of two softmax weights: `lo` in the low half (the earlier key), `hi` in the high half.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t packed;
