@@ -919,6 +919,9 @@ hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_sto
     const int tokens_per_tile = kRows / shape.group;
     args.mtiles = (tokens + tokens_per_tile - 1) / tokens_per_tile;
     args.n_items = args.mtiles * shape.kv_heads;
+    args.magic_kv_heads = division_magic(uint32_t(shape.kv_heads), uint32_t(args.n_items));
+    args.magic_chunks = 0;
+    args.magic_world = division_magic(uint32_t(std::max(cache.map.world, 1)), 1u << 24);
     if (shape.head_dim == 64) return launch_tc<64>(ctx, args, layer, stream);
     if (shape.head_dim == 128) return launch_tc<128>(ctx, args, layer, stream);
     return launch_tc256(ctx, layer.tmap_k, layer.tmap_v, &args, args.n_items, stream);
@@ -969,6 +972,9 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
     args.meta = meta;
     args.chunks = (max_tiles + args.tiles_per_item - 1) / args.tiles_per_item;
     args.n_items = args.chunks * shape.kv_heads * n_seq;
+    args.magic_chunks = division_magic(uint32_t(args.chunks), uint32_t(args.n_items));
+    args.magic_kv_heads = division_magic(uint32_t(shape.kv_heads), uint32_t(args.n_items));
+    args.magic_world = division_magic(uint32_t(std::max(cache.map.world, 1)), 1u << 24);
     hc_status st = shape.head_dim == 64 ? launch_tc<64>(ctx, args, layer, stream)
                    : shape.head_dim == 128 ? launch_tc<128>(ctx, args, layer, stream)
                    : launch_tc256(ctx, layer.tmap_k, layer.tmap_v, &args, args.n_items, stream);

@@ -92,8 +92,8 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         if (lane == 0) {
             uint32_t t = 0;
             bool ok = true;
-            for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item)) {
-                const TcItem w = decode_item(args, item);
+            for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk)) {
+                const TcItem& w = walk.w;
                 const int plane = w.seq * args.kv_heads + w.kv_head;
                 for (int j = 0; j < w.n_tiles; ++j, ++t) {
                     const int row0 = row_of_tile(args.map, w.tile_first + j * world);
@@ -142,8 +142,8 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
             };
             uint32_t t = 0, it = 0;
             bool ok = true;
-            for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item), ++it) {
-                const int n_tiles = decode_item(args, item).n_tiles;
+            for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk), ++it) {
+                const int n_tiles = walk.w.n_tiles;
                 if (!mbar_wait(&bars->q_full, it & 1, abort_flag, args.status, 4)) break;
                 tc_fence_after();
                 ok = issue_qk(t, n_tiles == 1);
@@ -181,8 +181,8 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         const float neg_inf = __int_as_float(0xff800000);
         uint32_t t = 0;
         bool ok = true;
-        for (int item = first_item(args); ok && item < args.n_items; item = next_item(args, item)) {
-            const TcItem w = decode_item(args, item);
+        for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk)) {
+            const TcItem& w = walk.w;
             const bool valid = t_local < w.valid_tokens;
             const bool warp_has_rows = quad * 32 < (w.valid_tokens << args.log_group);
             const int pos = valid ? w.first_pos + t_local : -1;
@@ -311,31 +311,35 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         };
         uint32_t t = 0, it = 0;
         bool ok = true;
-        int item = first_item(args);
-        if (half == 0 && item < args.n_items) stage_q(decode_item(args, item));
-        while (ok && item < args.n_items) {
-            const TcItem w = decode_item(args, item);
-            const int nxt = next_item(args, item);
+        TcItemIter walk = items_begin(args);
+        if (half == 0 && walk.item < args.n_items) stage_q(walk.w);
+        // The head's sink is fetched one item ahead (prefill only: decode writes raw partials).
+        const bool wants_sink = args.count_sink && args.sinks != nullptr && !args.decode;
+        uint16_t sink_bits = kNoSinkBits;
+        if (wants_sink && walk.item < args.n_items) sink_bits = args.sinks[walk.w.kv_head * G + g];
+        while (ok && walk.item < args.n_items) {
+            const TcItem w = walk.w;
+            items_next(args, walk);
             const int head = w.kv_head * G + g;
             const bool valid = t_local < w.valid_tokens;
             const bool warp_has_rows = quad * 32 < (w.valid_tokens << args.log_group);
             float M, L;
             if (args.count_sink) {
-                const uint16_t bits = args.sinks ? args.sinks[head] : kNoSinkBits;
-                M = __fmul_rn(bf16_bits_to_float(bits), kLog2e);
+                M = __fmul_rn(bf16_bits_to_float(sink_bits), kLog2e);
                 L = 1.0f;
             } else {
                 M = kEmptyMax;
                 L = 0.0f;
             }
+            if (wants_sink && walk.item < args.n_items) sink_bits = args.sinks[walk.w.kv_head * G + g];
             float A[128];
             #pragma unroll
             for (int i = 0; i < 128; ++i) A[i] = 0.0f;
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
-                if (half == 0 && j == w.n_tiles - 1 && nxt < args.n_items) {
+                if (half == 0 && j == w.n_tiles - 1 && walk.item < args.n_items) {
                     // The item's last S has been issued: its Q tile is free for the next item's.
                     if (!mbar_wait(&bars->q_empty, it & 1, abort_flag, args.status, 10)) { ok = false; break; }
-                    stage_q(decode_item(args, nxt));
+                    stage_q(walk.w);
                 }
                 if (!mbar_wait(&bars->o_full, t & 1, abort_flag, args.status, 9)) { ok = false; break; }
                 tc_fence_after();
@@ -426,7 +430,6 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
                     }
                 }
             }
-            item = nxt;
             ++it;
         }
     }

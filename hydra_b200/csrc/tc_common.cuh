@@ -33,8 +33,20 @@ struct TcArgs {
     float* part_o;            // fp32 [rows][part_tiles][d]
     float* part_ml;           // fp32 [rows][part_tiles][2]
     int part_tiles;
+    // Multipliers for the divisions of decode_item (see fast_div); 0 = divide the ordinary way.
+    uint32_t magic_chunks, magic_kv_heads, magic_world;
     BatchMeta meta;
 };
+
+// n / d for the small operands of the item list: with magic = ceil(2^32 / d) the high word of
+// n * magic is the quotient whenever n * d < 2^32, which the host checks before it sets a magic.
+__host__ __device__ inline uint32_t division_magic(uint32_t d, uint32_t n_max) {
+    if (d <= 1 || uint64_t(n_max) * d >= (1ull << 32)) return 0;
+    return uint32_t(((1ull << 32) + d - 1) / d);
+}
+__device__ __forceinline__ int fast_div(int n, int d, uint32_t magic) {
+    return magic != 0 ? int(__umulhi(uint32_t(n), magic)) : n / d;
+}
 
 
 struct TcItem {
@@ -53,18 +65,19 @@ __device__ __forceinline__ TcItem decode_item(const TcArgs& args, int index) {
     const int tokens_per_tile = kRows >> args.log_group;
     int chunk = 0;
     if (args.decode) {
-        chunk = index % args.chunks;
-        const int rest = index / args.chunks;
-        w.kv_head = rest % args.kv_heads;
-        const int b = rest / args.kv_heads;
+        const int rest = fast_div(index, args.chunks, args.magic_chunks);
+        chunk = index - rest * args.chunks;
+        const int b = fast_div(rest, args.kv_heads, args.magic_kv_heads);
+        w.kv_head = rest - b * args.kv_heads;
         w.row0 = b;
         w.valid_tokens = 1;
         w.first_pos = args.meta.pos[b];
         w.seq = args.meta.seq[b];
     } else {
         // Longest key ranges first: descending row tile, the kv heads of one row tile adjacent.
-        w.kv_head = index % args.kv_heads;
-        const int mtile = args.mtiles - 1 - index / args.kv_heads;
+        const int tile_index = fast_div(index, args.kv_heads, args.magic_kv_heads);
+        w.kv_head = index - tile_index * args.kv_heads;
+        const int mtile = args.mtiles - 1 - tile_index;
         w.row0 = mtile * tokens_per_tile;
         w.valid_tokens = min(tokens_per_tile, args.tokens - w.row0);
         w.first_pos = args.first_position + w.row0;
@@ -76,7 +89,8 @@ __device__ __forceinline__ TcItem decode_item(const TcArgs& args, int index) {
     int tile_first = lo_first / kTileKeys;
     const int tile_last = last_pos / kTileKeys;
     if (world > 1) tile_first += ((args.map.rank - tile_first % world) + world) % world;
-    int n_tiles = tile_first > tile_last ? 0 : (tile_last - tile_first) / world + 1;
+    int n_tiles = tile_first > tile_last ? 0
+                  : (world > 1 ? fast_div(tile_last - tile_first, world, args.magic_world) : tile_last - tile_first) + 1;
     w.ordinal0 = 0;
     if (args.decode) {
         w.ordinal0 = chunk * args.tiles_per_item;
