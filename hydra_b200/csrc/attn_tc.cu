@@ -935,10 +935,12 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
     const int world = cache.map.world > 1 ? cache.map.world : 1;
     int max_tiles = 0;
     long long total_tiles = 0;
+    int seq_tile_count[kMaxBatch];
     for (int b = 0; b < n_seq; ++b) {
         const int lo = shape.window > 0 ? std::max(0, meta.pos[b] - shape.window + 1) : 0;
         int n = meta.pos[b] / kTileKeys - lo / kTileKeys + 1;
         if (world > 1) n = (n + world - 1) / world + 1;
+        seq_tile_count[b] = n;
         max_tiles = std::max(max_tiles, n);
         total_tiles += n;
     }
@@ -962,8 +964,11 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
     args.ep = ep;
     args.status = ctx->status_dev;
     args.decode = 1;
-    // Items of consecutive tiles, about eight per CTA so that the static round-robin balances.  The head_dim 256 kernel does not look ahead across items: about one item per CTA.
-    const long long target = (shape.head_dim == 256 ? 1LL : 8LL) * std::max(ctx->sm_count, 1);
+    // Items of consecutive tiles, about six per CTA so that the static round-robin balances (measured
+    // best of 3 .. 12 on uniform and ragged batches).  The head_dim 256 kernel does not look ahead
+    // across items: about one item per CTA.
+    const long long items_per_sm = shape.head_dim == 256 ? 1LL : 6LL;
+    const long long target = items_per_sm * std::max(ctx->sm_count, 1);
     long long per = (total_tiles * shape.kv_heads + target - 1) / target;
     args.tiles_per_item = int(std::min<long long>(std::max<long long>(per, 1), 64));
     args.part_o = ws.part_o;
@@ -972,6 +977,24 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
     args.meta = meta;
     args.chunks = (max_tiles + args.tiles_per_item - 1) / args.tiles_per_item;
     args.n_items = args.chunks * shape.kv_heads * n_seq;
+    if (world <= 1) {
+        // Per-sequence item lists: each sequence's tiles in runs of one size, about `tiles_per_item`.
+        args.per_seq = 1;
+        int next = 0;
+        for (int b = 0; b < n_seq; ++b) {
+            const int tiles = std::max(seq_tile_count[b], 1);
+            const int want = (tiles + args.tiles_per_item - 1) / args.tiles_per_item;
+            const int run = (tiles + want - 1) / want;               // tiles per run, balanced
+            const int chunks = (tiles + run - 1) / run;              // no empty run
+            args.item_start[b] = next;
+            args.seq_chunks[b] = static_cast<unsigned short>(chunks);
+            args.seq_tiles[b] = static_cast<unsigned short>(run);
+            args.seq_magic[b] = division_magic(uint32_t(chunks), uint32_t(chunks) * uint32_t(shape.kv_heads));
+            next += chunks * shape.kv_heads;
+        }
+        for (int b = n_seq; b <= kMaxBatch; ++b) args.item_start[b] = next;
+        args.n_items = next;
+    }
     args.magic_chunks = division_magic(uint32_t(args.chunks), uint32_t(args.n_items));
     args.magic_kv_heads = division_magic(uint32_t(shape.kv_heads), uint32_t(args.n_items));
     args.magic_world = division_magic(uint32_t(std::max(cache.map.world, 1)), 1u << 24);

@@ -35,6 +35,15 @@ struct TcArgs {
     int part_tiles;
     // Multipliers for the divisions of decode_item (see fast_div); 0 = divide the ordinary way.
     uint32_t magic_chunks, magic_kv_heads, magic_world;
+    // Decode, per-sequence item lists (per_seq != 0; used when the cache is not sequence-sharded):
+    // sequence b's key tiles are cut into seq_chunks[b] runs of seq_tiles[b] tiles (the last one may
+    // be shorter, never empty), so ragged batches leave no empty items and the runs of one sequence
+    // are of one size.  Its items, kv head major, start at item_start[b].
+    int per_seq;
+    int item_start[kMaxBatch + 1];
+    unsigned short seq_chunks[kMaxBatch];
+    unsigned short seq_tiles[kMaxBatch];
+    uint32_t seq_magic[kMaxBatch];       // division by seq_chunks[b]
     BatchMeta meta;
 };
 
@@ -64,11 +73,27 @@ __device__ __forceinline__ TcItem decode_item(const TcArgs& args, int index) {
     TcItem w;
     const int tokens_per_tile = kRows >> args.log_group;
     int chunk = 0;
+    int tiles_per_item = args.tiles_per_item;
     if (args.decode) {
-        const int rest = fast_div(index, args.chunks, args.magic_chunks);
-        chunk = index - rest * args.chunks;
-        const int b = fast_div(rest, args.kv_heads, args.magic_kv_heads);
-        w.kv_head = rest - b * args.kv_heads;
+        int b;
+        if (args.per_seq) {
+            int lo = 0, hi = args.tokens;                 // item_start[lo] <= index < item_start[hi]
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (index >= args.item_start[mid]) lo = mid; else hi = mid;
+            }
+            b = lo;
+            const int local = index - args.item_start[b];
+            const int chunks = args.seq_chunks[b];
+            w.kv_head = fast_div(local, chunks, args.seq_magic[b]);
+            chunk = local - w.kv_head * chunks;
+            tiles_per_item = args.seq_tiles[b];
+        } else {
+            const int rest = fast_div(index, args.chunks, args.magic_chunks);
+            chunk = index - rest * args.chunks;
+            b = fast_div(rest, args.kv_heads, args.magic_kv_heads);
+            w.kv_head = rest - b * args.kv_heads;
+        }
         w.row0 = b;
         w.valid_tokens = 1;
         w.first_pos = args.meta.pos[b];
@@ -93,9 +118,9 @@ __device__ __forceinline__ TcItem decode_item(const TcArgs& args, int index) {
                   : (world > 1 ? fast_div(tile_last - tile_first, world, args.magic_world) : tile_last - tile_first) + 1;
     w.ordinal0 = 0;
     if (args.decode) {
-        w.ordinal0 = chunk * args.tiles_per_item;
+        w.ordinal0 = chunk * tiles_per_item;
         tile_first += w.ordinal0 * world;
-        n_tiles = min(args.tiles_per_item, n_tiles - w.ordinal0);
+        n_tiles = min(tiles_per_item, n_tiles - w.ordinal0);
     }
     w.tile_first = tile_first;
     w.n_tiles = n_tiles;
