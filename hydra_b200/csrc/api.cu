@@ -244,9 +244,11 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
     return HC_OK;
 }
 
+// With k_fused / v_fused set (hc_layer_step, one token) the K/V append rides in the Q prologue's launch.
 hc_status decode_impl(hc_context* ctx, hc_kv_cache* cache, int layer, const int* seq_ids,
                       const int* positions, int n_seq, const void* q, void* out,
-                      const hc_attn_params* p, bool partial_mode, cudaStream_t stream) {
+                      const hc_attn_params* p, bool partial_mode, cudaStream_t stream,
+                      const void* k_fused = nullptr, const void* v_fused = nullptr) {
     if (!ctx || !q || !out || !seq_ids || !positions) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
     hc_status st = validate_params(cache, layer, p);
     if (st != HC_OK) return st;
@@ -274,18 +276,25 @@ hc_status decode_impl(hc_context* ctx, hc_kv_cache* cache, int layer, const int*
         }
         const unsigned char* q_rows = offset_rows(q, size_t(start), size_t(p->q_heads) * d * mult, p->io_dtype);
         const uint16_t* q_bf16 = reinterpret_cast<const uint16_t*>(q_rows);
-        if (prep) {
+        if (prep || k_fused) {
             PrepArgs args{};
             fill_common(args, p);
-            fill_q_job(args.job[0], p, q_rows, cache->ws.qprep);
-            args.n_jobs = 1;
+            int jobs = 0;
+            if (prep) fill_q_job(args.job[jobs++], p, q_rows, cache->ws.qprep);
+            if (k_fused) {
+                const size_t kv_row = size_t(p->kv_heads) * d;
+                fill_kv_jobs(args, jobs, p, offset_rows(k_fused, size_t(start), kv_row, p->io_dtype),
+                             offset_rows(v_fused, size_t(start), kv_row, p->io_dtype));
+                jobs += 2;
+            }
+            args.n_jobs = jobs;
             args.tokens = count;
             args.batched = 1;
             args.meta = meta;
             args.cache = view;
             st = launch_prepare(ctx, args, stream);
             if (st != HC_OK) return st;
-            q_bf16 = cache->ws.qprep;
+            if (prep) q_bf16 = cache->ws.qprep;
         }
         EpilogueArgs ep{};
         ep.io_dtype = p->io_dtype;
@@ -974,12 +983,14 @@ hc_status hc_layer_step(hc_context* ctx, hc_kv_cache* cache, int layer, int seq,
         return prefill_impl(ctx, cache, layer, seq, q, out, tokens, first_position, params, false,
                             static_cast<cudaStream_t>(stream), k, v);
     }
+    if (tokens == 1) {
+        if (!seq_ok(cache, seq)) return fail(HC_INVALID_ARGUMENT, "sequence index out of range");
+        const int position = first_position;
+        return decode_impl(ctx, cache, layer, &seq, &position, 1, q, out, params, false,
+                           static_cast<cudaStream_t>(stream), k, v);
+    }
     st = hc_kv_append(ctx, cache, layer, seq, k, v, tokens, first_position, params, stream);
     if (st != HC_OK) return st;
-    if (tokens == 1) {
-        const int position = first_position;
-        return hc_attention_decode(ctx, cache, layer, &seq, &position, 1, q, out, params, stream);
-    }
     return hc_attention_prefill(ctx, cache, layer, seq, q, out, tokens, first_position, params, stream);
 }
 

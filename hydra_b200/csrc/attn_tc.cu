@@ -68,7 +68,10 @@ struct TcLayout {
     static constexpr int kRegsFold = kRowInRegs ? 160 : 232;
     static constexpr int kTmemCols = 512;
     static constexpr int kOnesBytes = kTileKeys * 128;       // a 128-row block of bf16 1.0 (16 KiB)
-    static constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + 2 * kStages * kTileBytes + kOnesBytes;
+    // Staging for the epilogue's coalesced stores: 4 warps x 32 rows x 128 bytes.  With d = 128 the
+    // block of ones is not used by any MMA and serves.
+    static constexpr int kEpiBytes = kSumOnTensor ? 4 * 32 * 128 : 0;
+    static constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + 2 * kStages * kTileBytes + kOnesBytes + kEpiBytes;
 };
 
 struct TcBarriers {
@@ -118,7 +121,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     unsigned char* k_smem = q_smem + 2 * LT::kQBytes;
     unsigned char* v_smem = k_smem + LT::kStages * LT::kTileBytes;
     unsigned char* ones_smem = v_smem + LT::kStages * LT::kTileBytes;   // 128 rows of bf16 1.0
-    TcBarriers* bars = reinterpret_cast<TcBarriers*>(ones_smem + LT::kOnesBytes);
+    unsigned char* epi_smem = LT::kEpiBytes > 0 ? ones_smem + LT::kOnesBytes : ones_smem;
+    TcBarriers* bars = reinterpret_cast<TcBarriers*>(ones_smem + LT::kOnesBytes + LT::kEpiBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -756,7 +760,42 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 if (threadIdx.x == 384) TC_EVT(t, 11)
             }
             if (!ok) break;
-            if (valid && !args.decode) {
+            if (!args.decode && warp_has_rows && !args.ep.write_partial && args.ep.gate_layout == HC_GATE_NONE &&
+                args.ep.io_dtype != HC_F32) {
+                // bf16 output without a gate (warp-uniform): rows go through shared memory so that a
+                // store instruction writes whole 128-byte lines (the G heads of a token are adjacent
+                // in memory) instead of 16 bytes of 32 different rows.
+                unsigned char* stage = epi_smem + (warp & 3) * (32 * 128);
+                uint16_t* out16 = reinterpret_cast<uint16_t*>(args.ep.out);
+                #pragma unroll
+                for (int b = 0; b < D / 64; ++b) {
+                    #pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        float r[8];
+                        #pragma unroll
+                        for (int u = 0; u < 8; ++u) r[u] = finish_value(A[b * 64 + ch * 8 + u], L, false, 0.0f);
+                        uint4 packed;
+                        packed.x = pack_bf16x2(r[0], r[1]);
+                        packed.y = pack_bf16x2(r[2], r[3]);
+                        packed.z = pack_bf16x2(r[4], r[5]);
+                        packed.w = pack_bf16x2(r[6], r[7]);
+                        *reinterpret_cast<uint4*>(stage + lane * 128 + ((ch ^ (lane & 7)) << 4)) = packed;
+                    }
+                    __syncwarp();
+                    #pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int rl = k * 4 + (lane >> 3), ch = lane & 7;
+                        const int row2 = quad * 32 + rl;
+                        const int t2 = row2 >> args.log_group;
+                        if (t2 < w.valid_tokens) {
+                            const size_t vec2 = size_t(w.row0 + t2) * args.q_heads + size_t(w.kv_head) * G + (row2 & (G - 1));
+                            const uint4 value = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((ch ^ (rl & 7)) << 4));
+                            *reinterpret_cast<uint4*>(out16 + vec2 * D + b * 64 + ch * 8) = value;
+                        }
+                    }
+                    __syncwarp();
+                }
+            } else if (valid && !args.decode) {
                 const size_t out_row = size_t(w.row0 + t_local);
                 if (args.ep.write_partial) {
                     float* dst = reinterpret_cast<float*>(args.ep.out) + (out_row * args.q_heads + head) * size_t(D + 2);
