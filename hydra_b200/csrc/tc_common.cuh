@@ -127,44 +127,6 @@ __device__ __forceinline__ TcItem decode_item(const TcArgs& args, int index) {
     return w;
 }
 
-// The next item of this CTA's list that has work, or n_items.
-__device__ __forceinline__ int next_item(const TcArgs& args, int index) {
-    for (index += gridDim.x; index < args.n_items; index += gridDim.x) {
-        if (decode_item(args, index).n_tiles > 0) return index;
-    }
-    return args.n_items;
-}
-__device__ __forceinline__ int first_item(const TcArgs& args) {
-    int index = blockIdx.x;
-    if (index < args.n_items && decode_item(args, index).n_tiles > 0) return index;
-    return index < args.n_items ? next_item(args, index) : args.n_items;
-}
-
-// A position in the stream of key tiles a CTA processes: tile j of the item with ordinal `it`.
-struct TcCursor {
-    int item;          // index in the work list, or n_items at the end
-    TcItem w;
-    int j;             // tile within the item
-    uint32_t t;        // ordinal of the tile in the CTA's stream
-    uint32_t it;       // ordinal of the item
-};
-__device__ __forceinline__ TcCursor cursor_begin(const TcArgs& args) {
-    TcCursor c{};
-    c.item = first_item(args);
-    if (c.item < args.n_items) c.w = decode_item(args, c.item);
-    return c;
-}
-__device__ __forceinline__ bool cursor_valid(const TcArgs& args, const TcCursor& c) { return c.item < args.n_items; }
-__device__ __forceinline__ void cursor_advance(const TcArgs& args, TcCursor& c) {
-    ++c.t;
-    if (++c.j >= c.w.n_tiles) {
-        c.item = next_item(args, c.item);
-        if (c.item < args.n_items) c.w = decode_item(args, c.item);
-        c.j = 0;
-        ++c.it;
-    }
-}
-
 // The walk over a CTA's items: each item is decoded once per role (its decoding costs a few integer
 // divisions, which a role pays on its critical path at every item boundary).
 struct TcItemIter {
