@@ -5,12 +5,13 @@ mirrors the reference's host interface on top of it.  Importing this package doe
 creating a `Context` does, and fails loudly without one or without the built library.
 """
 from . import capi
-from .backend import (AllocationFailed, AttentionBackend, AttnParams, BadRewind, CacheOverflow,
-                      Context, DimensionMismatch, HydraCudaError, KVCache, RopeTable,
-                      UnsupportedPattern, inverse_frequencies, yarn_inverse_frequencies)
+from .backend import (AllocationFailed, AttentionBackend, AttnParams, BadRewind, CacheOverflow, CommError,
+                      Context, DimensionMismatch, HydraCudaError, KVCache, NcclCommunicator, RopeTable,
+                      Shard, UnsupportedPattern, inverse_frequencies, yarn_inverse_frequencies)
 
 __all__ = [
-    "capi", "AllocationFailed", "AttentionBackend", "AttnParams", "BadRewind", "CacheOverflow",
-    "Context", "DimensionMismatch", "HydraCudaError", "KVCache", "RopeTable", "UnsupportedPattern",
+    "capi", "AllocationFailed", "AttentionBackend", "AttnParams", "BadRewind", "CacheOverflow", "CommError",
+    "Context", "DimensionMismatch", "HydraCudaError", "KVCache", "NcclCommunicator", "RopeTable", "Shard",
+    "UnsupportedPattern",
     "inverse_frequencies", "yarn_inverse_frequencies",
 ]

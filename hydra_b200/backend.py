@@ -44,13 +44,19 @@ class BadRewind(HydraCudaError):             # the precondition of KVCache.rewin
     pass
 
 
+class CommError(HydraCudaError):             # a sharded call given inconsistent rank data, or NCCL failed
+    pass
+
+
 _ERRORS = {
     capi.HC_ALLOC_FAILED: AllocationFailed,
     capi.HC_KV_OVERFLOW: CacheOverflow,
     capi.HC_DIM_MISMATCH: DimensionMismatch,
     capi.HC_UNSUPPORTED: UnsupportedPattern,
     capi.HC_BAD_REWIND: BadRewind,
+    capi.HC_COMM_ERROR: CommError,
 }
+
 
 
 def _check(status: int) -> None:
@@ -284,6 +290,68 @@ class KVCache:
             pass
 
 
+class NcclCommunicator:
+    """An ncclComm_t of this process's own, made with the NCCL that the library links (ctypes over
+    libnccl.so.2): rank 0 draws the unique id, `exchange(bytes) -> bytes` hands it to the other ranks
+    (a broadcast over whatever channel the host already has, e.g. torch.distributed), then every rank
+    joins.  The device of the calling thread must already be the rank's GPU."""
+
+    UNIQUE_ID_BYTES = 128
+
+    def __init__(self, rank: int, world: int, exchange):
+        import glob
+        import os
+        from . import build as lib_build
+        _, lib_dir = lib_build.nccl_paths()
+        names = sorted(glob.glob(os.path.join(lib_dir, "libnccl.so*"))) if lib_dir else []
+        self._nccl = ctypes.CDLL(names[0] if names else "libnccl.so.2")
+        self._nccl.ncclGetErrorString.restype = ctypes.c_char_p
+        # ncclUniqueId is a 128-byte struct, taken by value by ncclCommInitRank (bytes, not a C string:
+        # it holds zeros).
+        class UniqueId(ctypes.Structure):
+            _fields_ = [("internal", ctypes.c_ubyte * self.UNIQUE_ID_BYTES)]
+        uid = UniqueId()
+        if rank == 0:
+            self._check(self._nccl.ncclGetUniqueId(ctypes.byref(uid)))
+        uid = UniqueId.from_buffer_copy(exchange(bytes(uid)))
+        comm = ctypes.c_void_p()
+        self._nccl.ncclCommInitRank.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, UniqueId, ctypes.c_int]
+        self._check(self._nccl.ncclCommInitRank(ctypes.byref(comm), world, uid, rank))
+        self.handle, self.rank, self.world = comm, rank, world
+
+    def _check(self, result: int) -> None:
+        if result != 0:
+            raise CommError(capi.HC_COMM_ERROR, self._nccl.ncclGetErrorString(result).decode())
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self._nccl.ncclCommDestroy.argtypes = [ctypes.c_void_p]
+            self._nccl.ncclCommDestroy(self.handle)
+            self.handle = None
+
+
+class Shard:
+    """This rank's place among the GPUs that share a model: hc_shard_create."""
+
+    def __init__(self, ctx: Context, mode: int, rank: int, world: int, comm=None, max_partial_bytes: int = 0):
+        self._lib = capi.load()
+        handle = ctypes.c_void_p()
+        comm_ptr = comm.handle if isinstance(comm, NcclCommunicator) else comm
+        _check(self._lib.hc_shard_create(ctx.handle if ctx is not None else None, comm_ptr, mode, rank, world,
+                                         max_partial_bytes, ctypes.byref(handle)))
+        self.handle = handle
+
+    def describe(self):
+        desc = capi.ShardDesc()
+        _check(self._lib.hc_shard_describe(self.handle, ctypes.byref(desc)))
+        return desc.mode, desc.rank, desc.world
+
+    def close(self) -> None:
+        if self.handle:
+            self._lib.hc_shard_destroy(self.handle)
+            self.handle = None
+
+
 class AttentionBackend:
     """The kernel protocol of ForwardEncoder / BatchEncoder, on CUDA."""
 
@@ -373,6 +441,25 @@ class AttentionBackend:
         _check(self._lib.hc_attention_combine(self.ctx.handle, _ptr(gathered), world, rows,
                                               _ptr(query), _ptr(output), ctypes.byref(s),
                                               _stream(stream)))
+
+    # The two steps and the exchange between them as one call (hc_attention_*_sharded).
+    def attention_sharded(self, shard, cache, layer, query, output, positions, params, seq_ids=None,
+                          stream=None) -> None:
+        if isinstance(positions, int):
+            positions = [positions]
+        if seq_ids is None:
+            seq_ids = list(range(len(positions))) if len(positions) > 1 else [0]
+        s = params.struct()
+        _check(self._lib.hc_attention_decode_sharded(self.ctx.handle, shard.handle, cache.handle, layer,
+                                                     _ints(seq_ids), _ints(positions), len(positions),
+                                                     _ptr(query), _ptr(output), ctypes.byref(s), _stream(stream)))
+
+    def attention_prefill_sharded(self, shard, cache, layer, query, output, tokens, first_position, params,
+                                  seq: int = 0, stream=None) -> None:
+        s = params.struct()
+        _check(self._lib.hc_attention_prefill_sharded(self.ctx.handle, shard.handle, cache.handle, layer, seq,
+                                                      _ptr(query), _ptr(output), tokens, first_position,
+                                                      ctypes.byref(s), _stream(stream)))
 
     # rmsNormHeads (ForwardEncoder.swift:535) / rmsNormHeadsBatch (BatchEncoder.swift:429)
     def rms_norm_heads(self, vector, scale, tokens: int, heads: int, head_dim: int, eps: float,

@@ -92,6 +92,13 @@ _PROTOTYPES = {
     "hc_attention_decode_partial": (c_int, [_P, _P, c_int, POINTER(c_int), POINTER(c_int), c_int,
                                             _P, _P, POINTER(AttnParamsStruct), _P]),
     "hc_attention_combine": (c_int, [_P, _P, c_int, c_int, _P, _P, POINTER(AttnParamsStruct), _P]),
+    "hc_shard_create": (c_int, [_P, _P, c_int, c_int, c_int, c_size_t, POINTER(_P)]),
+    "hc_shard_destroy": (None, [_P]),
+    "hc_shard_describe": (c_int, [_P, POINTER(ShardDesc)]),
+    "hc_attention_decode_sharded": (c_int, [_P, _P, _P, c_int, POINTER(c_int), POINTER(c_int), c_int, _P, _P,
+                                            POINTER(AttnParamsStruct), _P]),
+    "hc_attention_prefill_sharded": (c_int, [_P, _P, _P, c_int, c_int, _P, _P, c_int, c_int,
+                                             POINTER(AttnParamsStruct), _P]),
     "hc_rms_norm_heads": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_float, c_int, _P]),
     "hc_apply_rope": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P]),
     "hc_qwen_split_query_gate": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
@@ -114,11 +121,12 @@ def load() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
+    path = os.environ.get("HYDRA_CUDA_LIBRARY", LIB_PATH)     # another build of the same library
+    if not os.path.exists(path):
         raise RuntimeError(
-            f"{LIB_PATH} is missing: build it with `python -m hydra_b200.build` "
+            f"{path} is missing: build it with `python -m hydra_b200.build` "
             "(nvcc, sm_100a).  There is no CPU fallback.")
-    lib = ctypes.CDLL(LIB_PATH)
+    lib = ctypes.CDLL(path)
     for name, (restype, argtypes) in _PROTOTYPES.items():
         fn = getattr(lib, name)          # AttributeError if the symbol is not exported
         fn.restype = restype

@@ -88,6 +88,17 @@ AttnShape shape_of(const hc_kv_cache* cache, const hc_attn_params* p, bool parti
     return shape;
 }
 
+// A sequence-sharded cache holds only this rank's key tiles: an entry point that writes a finished
+// output from it would normalise over a fraction of the keys, silently.  Only the partial forms,
+// whose results hc_attention_combine folds over the ranks, may read it.
+hc_status check_shard_mode(const hc_kv_cache* cache, bool partial_mode) {
+    if (!partial_mode && cache->shard.mode == HC_SHARD_SEQUENCE && cache->shard.world > 1) {
+        return fail(HC_UNSUPPORTED, "this cache is sequence-sharded over " + std::to_string(cache->shard.world) +
+                                        " ranks: use the _partial entry points and hc_attention_combine");
+    }
+    return HC_OK;
+}
+
 bool needs_q_prepare(const hc_attn_params* p) {
     return p->io_dtype != HC_BF16 || p->norm_q != 0 || p->rope != nullptr ||
            p->gate_layout == HC_GATE_INTERLEAVED;
@@ -188,6 +199,8 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
     if (st != HC_OK) return st;
     if (tokens == 0) return HC_OK;
 
+    st = check_shard_mode(cache, partial_mode);
+    if (st != HC_OK) return st;
     const AttnShape shape = shape_of(cache, p, partial_mode);
     const CacheView view = view_of(cache, L);
     const bool tensor = use_tensor_path(p, shape, &st);
@@ -259,6 +272,8 @@ hc_status decode_impl(hc_context* ctx, hc_kv_cache* cache, int layer, const int*
         st = check_positions(cache, L, positions[b], 1, p);
         if (st != HC_OK) return st;
     }
+    st = check_shard_mode(cache, partial_mode);
+    if (st != HC_OK) return st;
     const AttnShape shape = shape_of(cache, p, partial_mode);
     const CacheView view = view_of(cache, L);
     const bool tensor = use_tensor_path(p, shape, &st);
@@ -266,9 +281,11 @@ hc_status decode_impl(hc_context* ctx, hc_kv_cache* cache, int layer, const int*
     const int d = p->head_dim;
     const int mult = p->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
     const bool prep = needs_q_prepare(p);
+    // A launch takes as many sequences as the prepared-query buffer has rows for.
+    const int per_launch = prep ? std::min(kMaxBatch, cache->ws.qprep_tokens) : kMaxBatch;
 
-    for (int start = 0; start < n_seq; start += kMaxBatch) {
-        const int count = std::min(kMaxBatch, n_seq - start);
+    for (int start = 0; start < n_seq; start += per_launch) {
+        const int count = std::min(per_launch, n_seq - start);
         BatchMeta meta{};
         for (int b = 0; b < count; ++b) {
             meta.seq[b] = seq_ids[start + b];
@@ -324,7 +341,7 @@ hc_status decode_impl(hc_context* ctx, hc_kv_cache* cache, int layer, const int*
 hc_status static_decode_inputs(hc_context* ctx, hc_kv_cache* cache, int layer, const int* seq_ids,
                                const int* positions, int n_seq, const void* q, void* out,
                                const hc_attn_params* p, AttnShape* shape, CacheView* view, BatchMeta* meta,
-                               EpilogueArgs* ep) {
+                               EpilogueArgs* ep, const hc_layer_store** store, bool* tensor) {
     if (!ctx || !q || !out || !seq_ids || !positions) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
     hc_status st = validate_params(cache, layer, p);
     if (st != HC_OK) return st;
@@ -348,6 +365,9 @@ hc_status static_decode_inputs(hc_context* ctx, hc_kv_cache* cache, int layer, c
     }
     *shape = shape_of(cache, p, false);
     *view = view_of(cache, L);
+    *store = &L;
+    *tensor = use_tensor_path(p, *shape, &st);          // the same choice hc_attention_decode makes
+    if (st != HC_OK) return st;
     ep->out = out;
     ep->io_dtype = p->io_dtype;
     ep->write_partial = 0;
@@ -394,6 +414,16 @@ hc_status hc_context_create(int device, hc_context** out) {
         return fail(HC_ALLOC_FAILED, std::string("context status word: ") + cudaGetErrorString(err));
     }
     *ctx->status_host = 0;
+    // The fixed scratch of hc_attention_decode_static: its address is looked up here, once, with this
+    // device current, which also makes the runtime load that module (and reserve the array) now
+    // rather than inside the first call that must not allocate.
+    const hc_status scratch = static_scratch_prepare(device, &ctx->static_scratch);
+    if (scratch != HC_OK) {
+        const std::string message = g_last_error;
+        hc_context_destroy(ctx);
+        g_last_error = message;
+        return scratch;
+    }
     *out = ctx;
     return HC_OK;
 }

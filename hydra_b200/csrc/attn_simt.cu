@@ -17,6 +17,9 @@
 // These kernels are the general fallback (and the only path for head_dim 512 or tiny test
 // shapes); the tcgen05 kernels in attn_tc.cu serve head_dim 64/128/256.
 
+#include <algorithm>
+#include <string>
+
 #include "internal.hpp"
 
 namespace hc {
@@ -580,34 +583,29 @@ hc_status launch_combine(hc_context* ctx, const float* gathered, int world, int 
 constexpr size_t kStaticScratchFloats = size_t(2) << 20;               // 8 MiB
 static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 
-// `g_static_scratch` in host code is only a handle: the device address comes from
-// cudaGetSymbolAddress, asked once per device with that device current.
-static float* static_scratch_address(int device, hc_status* status) {
-    static float* address[64] = {};
-    *status = HC_OK;
-    if (device < 0 || device >= 64) {
-        *status = fail(HC_INVALID_ARGUMENT, "device index out of range");
-        return nullptr;
+// `g_static_scratch` in host code is only a handle, not a device address: a kernel given it would
+// fault or, where the GPU can reach host memory, quietly use the wrong memory.  The device address
+// comes from cudaGetSymbolAddress, asked at context creation with that device current.
+hc_status static_scratch_prepare(int device, float** address) {
+    *address = nullptr;
+    int current = -1;
+    cudaError_t err = cudaGetDevice(&current);
+    if (err == cudaSuccess && current != device) {
+        return fail(HC_INVALID_ARGUMENT, "static scratch: device " + std::to_string(device) + " is not current");
     }
-    if (!address[device]) {
-        int current = -1;
-        cudaError_t err = cudaGetDevice(&current);
-        if (err == cudaSuccess && current != device) err = cudaSetDevice(device);
-        void* ptr = nullptr;
-        if (err == cudaSuccess) err = cudaGetSymbolAddress(&ptr, g_static_scratch);
-        if (err != cudaSuccess || !ptr) {
-            *status = check_cuda(err == cudaSuccess ? cudaErrorInvalidSymbol : err, "address of the static decode scratch");
-            return nullptr;
-        }
-        address[device] = static_cast<float*>(ptr);
+    void* ptr = nullptr;
+    if (err == cudaSuccess) err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess || !ptr) {
+        return check_cuda(err == cudaSuccess ? cudaErrorInvalidSymbol : err, "address of the static decode scratch");
     }
-    return address[device];
+    *address = static_cast<float*>(ptr);
+    return HC_OK;
 }
 
 hc_status static_decode_inputs(hc_context* ctx, hc_kv_cache* cache, int layer, const int* seq_ids,
                                const int* positions, int n_seq, const void* q, void* out,
                                const hc_attn_params* p, AttnShape* shape, CacheView* view, BatchMeta* meta,
-                               EpilogueArgs* ep);
+                               EpilogueArgs* ep, const hc_layer_store** store, bool* tensor);
 
 }  // namespace hc
 
@@ -623,9 +621,12 @@ hc_status hc_attention_decode_static(hc_context* ctx, hc_kv_cache* cache, int la
     CacheView view{};
     BatchMeta meta{};
     EpilogueArgs ep{};
+    const hc_layer_store* store = nullptr;
+    bool tensor = false;
     hc_status st = static_decode_inputs(ctx, cache, layer, seq_ids, positions, n_seq, q, out, params, &shape,
-                                        &view, &meta, &ep);
+                                        &view, &meta, &ep, &store, &tensor);
     if (st != HC_OK) return st;
+    if (!ctx->static_scratch) return fail(HC_CUDA_ERROR, "this context has no static scratch address");
     int max_tiles = 0;
     for (int b = 0; b < n_seq; ++b) {
         int lo, first_tile, last_tile;
@@ -641,15 +642,19 @@ hc_status hc_attention_decode_static(hc_context* ctx, hc_kv_cache* cache, int la
                                         " bytes of partials, the fixed scratch holds " +
                                         std::to_string(kStaticScratchFloats * 4));
     }
-    float* scratch = static_scratch_address(ctx->device, &st);
-    if (!scratch) return st;
     // Every partial the merge reads is written by this call's split kernel first, so nothing in the
     // array has to start at zero.
     Workspace ws;
-    ws.part_o = scratch;
-    ws.part_ml = scratch + o_floats;
+    ws.part_o = ctx->static_scratch;
+    ws.part_ml = ctx->static_scratch + o_floats;
     ws.part_o_floats = o_floats;
     ws.part_ml_floats = rows * max_tiles * 2;
+    // The same kernels, in the same order, as hc_attention_decode: only the partials live elsewhere,
+    // so the two entry points return the same bits.
+    if (tensor) {
+        return tc_decode(ctx, shape, *store, view, meta, n_seq, static_cast<const uint16_t*>(q), ws, ep,
+                         static_cast<cudaStream_t>(stream));
+    }
     return simt_decode(ctx, shape, view, meta, n_seq, static_cast<const uint16_t*>(q), ws, ep,
                        static_cast<cudaStream_t>(stream));
 }

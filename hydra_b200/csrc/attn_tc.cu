@@ -18,9 +18,10 @@
 //                              instruction.  Warp 3: copies each item's Q tile into the swizzled
 //                              operand layout, two items ahead.
 //   warpgroups 1-2 (warps 4-11) softmax, thread = row; the groups take alternate tiles.  S from
-//                              tensor memory, causal / window mask, row maximum, then (the two
-//                              groups strictly in turn) P = bf16(exp2(..)) back into tensor memory
-//                              over S.  In decode the 16 real rows are read with the 16x256b shape,
+//                              tensor memory, causal / window mask, row maximum, then
+//                              P = bf16(exp2(..)) back into tensor memory over S.  What paces a
+//                              tile is the exp2 unit: 16 results per clock per SM, 1024 clocks for
+//                              128 x 128; the two groups' exp2 phases are left free to overlap.  In decode the 16 real rows are read with the 16x256b shape,
 //                              four threads per row.
 //   warpgroup 3 (warps 12-15)   fold: O_j from tensor memory folded into the row's running (M, L, A)
 //                              in registers (prefill) or written out as the tile's partial
@@ -79,36 +80,12 @@ struct TcBarriers {
     uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
     uint64_t s_full[3], p_full[3], pv_done[3];   // per S buffer; pv_done: P V has read the buffer's P
     uint64_t o_full, o_free;
-    uint64_t xu_turn[2];      // the softmax warpgroups take turns in the exp2 phase
     uint32_t tmem_base;
     int abort_flag;
     float mm[8][kRows];       // per-tile scaled maxima, softmax -> fold (ring of 8 tiles)
     float l[8][kRows];        // per-tile row sums (when not summed on the tensor core)
 };
 
-// One unit of work of a CTA.
-// Optional timeline for bring-up builds (-DHC_TC_TRACE): nanosecond stamps of a few events per CTA.
-#ifdef HC_TC_TRACE
-__device__ unsigned long long hc_tc_trace[256 * 16 * 4];
-__device__ __forceinline__ void tc_trace(int slot) {
-    unsigned long long now;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-    if (blockIdx.x < 256 && hc_tc_trace[blockIdx.x * 16 + slot] == 0) hc_tc_trace[blockIdx.x * 16 + slot] = now;
-}
-#define TC_TRACE(slot) tc_trace(slot)
-// Cycle accounting of one thread: TC_LAP(k) adds the cycles since the previous lap to bucket k.
-#define TC_LAP_DECL long long lap_last = clock64(); long long lap_acc[6] = {0, 0, 0, 0, 0, 0};
-#define TC_LAP(k) { const long long lap_now = clock64(); lap_acc[k] += lap_now - lap_last; lap_last = lap_now; }
-#define TC_LAP_STORE(base) { for (int lap_i = 0; lap_i < 6; ++lap_i) hc_tc_trace[(blockIdx.x & 255) * 16 + 16 * 256 * (base) + lap_i] = (unsigned long long)lap_acc[lap_i]; }
-// Clock stamps of the events of stream tiles 16..23 of CTA 0 (rows 200..207 of the timeline plane).
-#define TC_EVT(t, id) { if (blockIdx.x == 0 && (t) >= 16u && (t) < 24u) hc_tc_trace[(200 + (t) - 16) * 16 + (id)] = (unsigned long long)clock64(); }
-#else
-#define TC_EVT(t, id) {}
-#define TC_TRACE(slot)
-#define TC_LAP_DECL
-#define TC_LAP(k) {}
-#define TC_LAP_STORE(base) {}
-#endif
 
 template <int D>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -133,11 +110,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
-        TC_TRACE(0);
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars->q_full[i], 1);
             mbar_init(&bars->q_empty[i], 1);
-            mbar_init(&bars->xu_turn[i], 128);
         }
         for (int i = 0; i < 3; ++i) {
             mbar_init(&bars->s_full[i], 1);
@@ -172,7 +147,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     // Everything above touched only this CTA's shared and tensor memory; from here on the kernel
     // reads what earlier kernels of the stream wrote (prepared q, the cache) and writes its outputs.
     pdl_wait();
-    if (threadIdx.x == 0) TC_TRACE(1);
 
     // Registers follow the work (setmaxnreg, first thing in each warpgroup's branch): the fold
     // warpgroup holds a row of O per thread, the control warpgroup needs almost none.
@@ -218,7 +192,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         constexpr uint32_t idesc_qk = instr_desc(kTileKeys, false);
         const uint64_t q_desc0 = smem_desc(smem_u32(q_smem), 16);
         const uint64_t k_desc0 = smem_desc(smem_u32(k_smem), 16);
-        TC_LAP_DECL
         uint32_t t = 0, it = 0;
         bool ok = true;
         for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk), ++it) {
@@ -233,8 +206,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             if (j == 0 && !mbar_wait(&bars->q_full[qb], (it >> 1) & 1, abort_flag, args.status, 4)) { ok = false; break; }
             if (!mbar_wait(&bars->k_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 3)) { ok = false; break; }
             tc_fence_after();
-            TC_LAP(0)
-            TC_EVT(t, 3)
             if (elect_one()) {
                 // Descriptors differ from the precomputed bases only in the 16-byte address field.
                 const uint64_t q_desc = q_desc0 + uint64_t((qb * LT::kQBytes) >> 4);
@@ -248,17 +219,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         mma_ss(s_tmem, q_desc + off, k_desc + off, idesc_qk, (b | ks) != 0 ? 1u : 0u);
                     }
                 }
-                TC_LAP(1)
                 tc_commit(&bars->k_empty[slot]);
                 tc_commit(&bars->s_full[sb]);
                 if (j + 1 == n_tiles) tc_commit(&bars->q_empty[qb]);   // the item's Q tile was read for the last time
-                TC_LAP(2)
             }
             __syncwarp();
-            TC_EVT(t, 4)
           }
         }
-        if (elect_one()) { TC_LAP_STORE(3) }
     } else if (warp == 2) {
         // ===== O issuer: O_t = P_t V_t (A = P from tensor memory) as soon as the tile's weights are
         // written and the fold has taken the previous tile out of the O buffer. =====
@@ -276,11 +243,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 const int slot = int(t % LT::kStages);
                 const int sb = int(t % LT::kSBufs);
                 if (!mbar_wait(&bars->p_full[sb], (t / LT::kSBufs) & 1, abort_flag, args.status, 5)) { ok = false; break; }
-                TC_EVT(t, 0)
                 if (!mbar_wait(&bars->v_full[slot], (t / LT::kStages) & 1, abort_flag, args.status, 6)) { ok = false; break; }
                 if (t >= 1 && !mbar_wait(&bars->o_free, (t - 1) & 1, abort_flag, args.status, 7)) { ok = false; break; }
                 tc_fence_after();
-                TC_EVT(t, 1)
                 if (elect_one()) {
                     const uint32_t v_addr = v_base + slot * LT::kTileBytes;
                     const uint32_t p_tmem = tmem + sb * kTileKeys;
@@ -296,7 +261,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     tc_commit(&bars->v_empty[slot]);
                 }
                 __syncwarp();
-                TC_EVT(t, 2)
             }
         }
     } else {
@@ -347,10 +311,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         const int t_local = row >> args.log_group;
         const uint32_t lane_base = uint32_t(quad * 32) << 16;
         const float neg_inf = __int_as_float(0xff800000);
-        const bool take_turns = !(args.decode && LT::kSumOnTensor);
         uint32_t t = 0;
         bool ok = true;
-        TC_LAP_DECL
         for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk)) {
             const TcItem& w = walk.w;
             const bool valid = t_local < w.valid_tokens;
@@ -361,15 +323,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 if (int(t & 1) != parity) continue;
                 const int sb = int(t % LT::kSBufs);
                 const uint32_t s_tmem = tmem + lane_base + sb * kTileKeys;
-                TC_LAP(5)
                 if (!mbar_wait(&bars->s_full[sb], (t / LT::kSBufs) & 1, abort_flag, args.status, 8)) { ok = false; break; }
-                TC_LAP(0)
-                if ((threadIdx.x & 127) == 0) TC_EVT(t, 5)
                 tc_fence_after();
                 if (!warp_has_rows) {
                     // No query row lives in this quadrant: its P rows stay whatever they were and the
                     // O rows they produce are never read (rows are independent).
-                    if (take_turns) mbar_arrive(&bars->xu_turn[parity ^ 1]);
                     tc_fence_before();
                     mbar_arrive(&bars->p_full[sb]);
                     continue;
@@ -389,7 +347,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     HC_TMEM_LD_16x256b_x8(s_tmem, v[0]);
                     HC_TMEM_LD_16x256b_x8(s_tmem + 64, v[1]);
                     tc_wait_ld();
-                    TC_LAP(1)
                     if (!(c_lo <= 0 && c_hi >= kTileKeys - 1)) {
                         #pragma unroll
                         for (int hb = 0; hb < 2; ++hb) {
@@ -429,7 +386,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                             if (q4 == 0) bars->mm[t & 7][(lane >> 2) + 8 * rs] = __fmul_rn(m, args.c);
                         }
                     }
-                    TC_LAP(2)
                     // st[2n + rs]: P column 4n + q4 of row lane/4 + 8 rs, the layout of the 16x128b store.
                     #pragma unroll
                     for (int hb = 0; hb < 2; ++hb) {
@@ -452,7 +408,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     tc_wait_st();
                     tc_fence_before();
                     mbar_arrive(&bars->p_full[sb]);
-                    TC_LAP(3)
                     continue;
                 }
                 const int c_lo = lo - key0;                  // visible columns: [c_lo, c_hi]
@@ -460,7 +415,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 const bool full = c_lo <= 0 && c_hi >= kTileKeys - 1;
                 if constexpr (LT::kRowInRegs) {
                     // The whole row of S in registers: one load, the maximum, the scaled differences
-                    // (two per instruction), and only then, in this group's turn, the exp2 unit's
+                    // (two per instruction), and then the exp2 unit's
                     // share: exp2, rounding to bf16 and the store of P.
                     uint32_t s[4][32];
                     HC_TMEM_LD32(s_tmem, s[0]);
@@ -492,17 +447,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         #pragma unroll
                         for (int i = 0; i < 16; ++i) fma2_inplace(s[q][2 * i], s[q][2 * i + 1], args.c, neg_mc);
                     }
-                    TC_LAP(2)
-                    if ((threadIdx.x & 127) == 0) TC_EVT(t, 6)
-                    const uint32_t own = t >> 1;             // ordinal of this tile among the group's tiles
-                    if (take_turns && (parity == 1 || own > 0)) {
-                        if (!mbar_wait(&bars->xu_turn[parity], (parity == 1 ? own : own - 1) & 1, abort_flag, args.status, 11)) {
-                            ok = false;
-                            break;
-                        }
-                    }
-                    TC_LAP(1)
-                    if ((threadIdx.x & 127) == 0) TC_EVT(t, 7)
                     #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         #pragma unroll
@@ -514,16 +458,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         }
                         HC_TMEM_ST16(s_tmem + q * 16, packed);
                     }
-                    if (take_turns) mbar_arrive(&bars->xu_turn[parity ^ 1]);
                     bars->mm[t & 7][row] = __fmul_rn(m, args.c);
-                    TC_LAP(3)
-                    if ((threadIdx.x & 127) == 0) TC_EVT(t, 8)
                     tc_wait_st();
                     tc_fence_before();
                     mbar_arrive(&bars->p_full[sb]);
-                    TC_LAP(4)
-                    if ((threadIdx.x & 127) == 0) TC_EVT(t, 9)
-                    if (lane == 0) TC_EVT(t, 12 + quad)
                     continue;
                 }
                 // The row is read twice, 32 columns at a time, in rolled loops: the maximum, then the
@@ -569,19 +507,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     }
                 }
                 const float neg_mc = -__fmul_rn((m == neg_inf) ? 0.0f : m, args.c);
-                TC_LAP(2)
-                if ((threadIdx.x & 127) == 0) TC_EVT(t, 6)
-                // The two groups enter the weights pass strictly in turn (group 0 first), which keeps
-                // them half a period apart instead of colliding in it and idling together.
-                const uint32_t own = t >> 1;                 // ordinal of this tile among the group's tiles
-                if (take_turns && (parity == 1 || own > 0)) {
-                    if (!mbar_wait(&bars->xu_turn[parity], (parity == 1 ? own : own - 1) & 1, abort_flag, args.status, 11)) {
-                        ok = false;
-                        break;
-                    }
-                }
-                TC_LAP(1)
-                if ((threadIdx.x & 127) == 0) TC_EVT(t, 7)
                 // Weights of one group of 32 columns; returns their sum when the tensor core does not.
                 auto group_weights = [&](const uint32_t (&s)[32], uint32_t dst) -> float {
                     uint32_t packed[16];
@@ -630,19 +555,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         if (h == 0) half_sum[0] = hs; else half_sum[1] = hs;
                     }
                 }
-                if (take_turns) mbar_arrive(&bars->xu_turn[parity ^ 1]);
                 if (!LT::kSumOnTensor) bars->l[t & 7][row] = __fadd_rn(half_sum[0], half_sum[1]);
                 bars->mm[t & 7][row] = __fmul_rn(m, args.c);
-                TC_LAP(3)
-                if ((threadIdx.x & 127) == 0) TC_EVT(t, 8)
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[sb]);
-                TC_LAP(4)
-                if ((threadIdx.x & 127) == 0) TC_EVT(t, 9)
             }
         }
-        if (threadIdx.x == 128) { TC_LAP_STORE(1) }
     } else {
         // ===== fold + epilogue: thread = row =====
         reg_alloc<LT::kRegsFold>();
@@ -660,7 +579,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         uint32_t t = 0, it = 0;
         bool ok = true;
         TcItemIter walk = items_begin(args);
-        TC_LAP_DECL
         // The head's sink is fetched one item ahead (prefill only: decode writes raw partials and the
         // merge kernel seeds the fold), so its latency never sits at an item's start.
         const bool wants_sink = args.count_sink && args.sinks != nullptr && !args.decode;
@@ -685,10 +603,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             #pragma unroll
             for (int i = 0; i < D; ++i) A[i] = 0.0f;
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
-                TC_LAP(5)
                 if (!mbar_wait(&bars->o_full, t & 1, abort_flag, args.status, 9)) { ok = false; break; }
-                TC_LAP(0)
-                if (threadIdx.x == 384) TC_EVT(t, 10)
                 tc_fence_after();
                 if (!warp_has_rows) {
                     tc_fence_before();
@@ -697,7 +612,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 }
                 const uint32_t o_tmem = tmem + lane_base + LT::kOCol0;
                 const uint32_t l_bits = tile_sum(o_tmem, t);   // valid after the first wait below
-                TC_LAP(1)
                 if (args.decode) {
                     // Split decode: the tile's partial goes to the workspace; merge_tiles_kernel folds.
                     const size_t prow = (size_t(w.row0) * args.q_heads + head) * args.part_tiles + (w.ordinal0 + j);
@@ -707,7 +621,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         HC_TMEM_LD32(o_tmem + hb * 64, o[0]);
                         HC_TMEM_LD32(o_tmem + hb * 64 + 32, o[1]);
                         tc_wait_ld();
-                        TC_LAP(2)
                         if (hb == D / 64 - 1) {
                             tc_fence_before();
                             mbar_arrive(&bars->o_free);
@@ -728,7 +641,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         args.part_ml[prow * 2] = bars->mm[t & 7][row];
                         args.part_ml[prow * 2 + 1] = __uint_as_float(l_bits);
                     }
-                    TC_LAP(3)
                     continue;
                 }
                 float Mn, a, b;
@@ -756,8 +668,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         }
                     }
                 }
-                TC_LAP(2)
-                if (threadIdx.x == 384) TC_EVT(t, 11)
             }
             if (!ok) break;
             if (!args.decode && warp_has_rows && !args.ep.write_partial && args.ep.gate_layout == HC_GATE_NONE &&
@@ -834,14 +744,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 }
             }
             ++it;
-            TC_LAP(3)
-        }
-        if (threadIdx.x == 384) { TC_LAP_STORE(2) }
-        if (threadIdx.x == 384) {
-#ifdef HC_TC_TRACE
-            hc_tc_trace[(blockIdx.x & 255) * 16 + 9] = 0;
-#endif
-            TC_TRACE(9);
         }
     }
 
@@ -852,7 +754,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     }
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0) TC_TRACE(10);
     if (warp == 1) tmem_dealloc(tmem, LT::kTmemCols);
 }
 
@@ -1044,16 +945,5 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
     return launch_merge(ctx, shape, meta, n_seq, ws, max_tiles, world, cache.map.rank, ep, stream);
 }
 
-#ifdef HC_TC_TRACE
-extern "C" __attribute__((visibility("default"))) int hc_debug_read_trace(unsigned long long* out, int clear) {
-    cudaDeviceSynchronize();
-    if (cudaMemcpyFromSymbol(out, hc_tc_trace, sizeof(hc_tc_trace)) != cudaSuccess) return -1;
-    if (clear) {
-        static unsigned long long zeros[256 * 16 * 4];
-        cudaMemcpyToSymbol(hc_tc_trace, zeros, sizeof(zeros));
-    }
-    return 0;
-}
-#endif
 
 }  // namespace hc

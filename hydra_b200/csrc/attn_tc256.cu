@@ -22,7 +22,6 @@
 namespace hc {
 namespace {
 
-#define TC_TRACE(slot)
 
 constexpr int kD = 256;
 constexpr int kBlocks256 = kD / 64;

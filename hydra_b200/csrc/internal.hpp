@@ -112,6 +112,7 @@ struct hc_context {
     uint64_t launches = 0;
     int* status_dev = nullptr;    // one word the kernels may set on a bounded-wait timeout
     int* status_host = nullptr;   // pinned mirror
+    float* static_scratch = nullptr;   // device address of the fixed scratch of hc_attention_decode_static
 };
 
 struct hc_rope_table {
@@ -172,6 +173,8 @@ hc_status launch_merge(hc_context* ctx, const AttnShape& shape, const BatchMeta&
                        cudaStream_t stream);
 hc_status launch_combine(hc_context* ctx, const float* gathered, int world, int rows, int q_heads,
                          int d, const EpilogueArgs& ep, cudaStream_t stream);
+// Device address of the fixed scratch array on `device` (which must be current).
+hc_status static_scratch_prepare(int device, float** address);
 
 // attn_tc.cu
 bool tc_supported(const AttnShape& shape);

@@ -56,6 +56,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     const long long start = clock64();
     for (;;) {
         if (mbar_try_wait_parked(bar, parity, 2000)) return true;
+        __nanosleep(64);      // a waiting warp that polls flat out takes issue slots from the working ones
         if (*abort_flag != 0) return false;
         if (static_cast<unsigned long long>(clock64() - start) > kWaitCycles) {
             *abort_flag = 1;

@@ -164,13 +164,10 @@ class Inputs:
                 entry["q"] = np.ascontiguousarray(q_all)                       # interleaved
             else:
                 entry["q"] = np.ascontiguousarray(q_all[:, q_slice]).reshape(-1, cfg.q_heads, d)
-            if not (src.ragged or src.prefilled):
-                entry["k"] = np.ascontiguousarray(project(wk, hidden)[:, kv_slice]).reshape(-1, cfg.kv_heads, d)
-                entry["v"] = np.ascontiguousarray(project(wv, hidden)[:, kv_slice]).reshape(-1, cfg.kv_heads, d)
-            else:
-                # The new token's own k, v come from its hidden state; the history is drawn directly.
-                entry["k"] = np.ascontiguousarray(project(wk, hidden)[:, kv_slice]).reshape(-1, cfg.kv_heads, d)
-                entry["v"] = np.ascontiguousarray(project(wv, hidden)[:, kv_slice]).reshape(-1, cfg.kv_heads, d)
+            # With a pre-filled history (C4, C5) these are the new token's own k, v; the history is drawn
+            # directly (see `history`).
+            entry["k"] = np.ascontiguousarray(project(wk, hidden)[:, kv_slice]).reshape(-1, cfg.kv_heads, d)
+            entry["v"] = np.ascontiguousarray(project(wv, hidden)[:, kv_slice]).reshape(-1, cfg.kv_heads, d)
             self.layers.append(entry)
         self.rng = rng
         self.lengths = ragged_lengths(src) if src.ragged else None

@@ -96,7 +96,10 @@ typedef struct hc_layer_desc {
  *                      matching query heads; nothing is exchanged inside attention.
  *   HC_SHARD_SEQUENCE: key tiles of 128 positions are dealt round-robin, tile j to rank j % world.
  *                      Each rank appends only the rows it owns, attends over them, and the ranks'
- *                      partial results are combined by hc_attention_combine. */
+ *                      partial results are combined by hc_attention_combine (or all in one call:
+ *                      hc_attention_decode_sharded).  The entry points that write a finished
+ *                      output refuse such a cache with HC_UNSUPPORTED: they would normalise over
+ *                      this rank's keys alone. */
 typedef enum hc_shard_mode { HC_SHARD_NONE = 0, HC_SHARD_HEADS = 1, HC_SHARD_SEQUENCE = 2 } hc_shard_mode;
 typedef struct hc_shard_desc {
     int mode;   /* hc_shard_mode */
@@ -280,8 +283,13 @@ HC_API hc_status hc_attention_decode(hc_context* ctx, hc_kv_cache* cache, int la
  *     none or HC_GATE_SEPARATE.  1 to 64 sequences; not for sequence-sharded caches.
  *   - A call whose partials (n_seq * q_heads * visible_tiles * (head_dim + 2) floats) exceed the
  *     limit is refused with HC_KV_OVERFLOW and a message that states both sizes.
- *   - The first call on a device looks the array's device address up (cudaGetSymbolAddress, with
- *     that device current).  Make that first call outside any stream capture.
+ *   - It runs the same kernels as hc_attention_decode (tcgen05 for head_dim 64, 128, 256, CUDA
+ *     cores otherwise, params->kernel_path honoured) with the partials redirected, so its output
+ *     equals hc_attention_decode's bit for bit.
+ *   - The array's device address is looked up by hc_context_create (cudaGetSymbolAddress, with the
+ *     context's device current), which also makes the CUDA runtime load the module that holds the
+ *     array: the 8 MiB are reserved when the context is created, not inside a later call.  Create
+ *     the context before starting a stream capture and before handing the device's memory away.
  *   - All calls share the array and it keeps the last call's contents.  Nothing in it needs to be
  *     zero beforehand: each call writes every partial before reading it.  Two calls that overlap on
  *     the GPU (different streams, no dependency) race on it: serialise them. */
@@ -314,6 +322,36 @@ HC_API hc_status hc_attention_decode_partial(hc_context* ctx, hc_kv_cache* cache
 HC_API hc_status hc_attention_combine(hc_context* ctx, const void* gathered, int world, int rows,
                                       const void* q, void* out, const hc_attn_params* params,
                                       void* stream);
+
+/* ---- shards: the same two steps as one call, the exchange inside the library ------------------ */
+
+/* This rank's place among the GPUs that share a model (no counterpart in the reference).
+ * `nccl_comm` is an ncclComm_t the caller initialised (ncclCommInitRank) and keeps alive; it is
+ * needed only for HC_SHARD_SEQUENCE over more than one rank (head shards exchange nothing inside
+ * attention) and its size and rank must agree with `world` and `rank`: a mismatch, like any
+ * inconsistent (mode, rank, world), is HC_COMM_ERROR.  `max_partial_bytes` is the largest
+ * hc_attention_partial_bytes(params, rows) a sharded call will need; the exchange buffers
+ * ((world + 1) times that) are allocated here, not on the step path. */
+typedef struct hc_shard hc_shard;
+HC_API hc_status hc_shard_create(hc_context* ctx, void* nccl_comm, int mode, int rank, int world,
+                                 size_t max_partial_bytes, hc_shard** out);
+HC_API void hc_shard_destroy(hc_shard* shard);
+/* The hc_shard_desc to create this rank's cache with. */
+HC_API hc_status hc_shard_describe(const hc_shard* shard, hc_shard_desc* desc);
+
+/* hc_attention_decode / hc_attention_prefill on a sharded cache, complete: for a sequence shard
+ * this rank's partial, ncclAllGather of the ranks' partials into this GPU's memory and the combine
+ * are enqueued on `stream` in that order, and every rank ends with the same bits in `out`.  For a
+ * head shard (or a world of one) they are the plain calls.  The cache must have been created with
+ * hc_shard_describe's description. */
+HC_API hc_status hc_attention_decode_sharded(hc_context* ctx, hc_shard* shard, hc_kv_cache* cache,
+                                             int layer, const int* seq_ids, const int* positions,
+                                             int n_seq, const void* q, void* out,
+                                             const hc_attn_params* params, void* stream);
+HC_API hc_status hc_attention_prefill_sharded(hc_context* ctx, hc_shard* shard, hc_kv_cache* cache,
+                                              int layer, int seq, const void* q, void* out,
+                                              int tokens, int first_position,
+                                              const hc_attn_params* params, void* stream);
 
 /* Stand-alone forms of the element-wise kernels, for runners that call them one by one as the
  * reference does.  In place on `vector` (io_dtype).

@@ -38,7 +38,9 @@ def load(path, name):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of a Neojarred/Hydra checkout>")
+    ref = sys.argv[1]
     here = os.path.dirname(os.path.abspath(__file__))
     gpt = load(os.path.join(ref, "tools", "gen_reference_fixtures.py"), "gen_reference_fixtures")
     gem = load(os.path.join(ref, "tools", "gen_gemma_fixtures.py"), "gen_gemma_fixtures")

@@ -38,10 +38,6 @@ def golden():
         return json.load(f)
 
 
-def both_paths(hb):
-    return [hb.capi.HC_PATH_SIMT, hb.capi.HC_PATH_AUTO]
-
-
 # ---- golden vectors, on the device ---------------------------------------------------------------
 
 @pytest.mark.parametrize("name", ["sdpa_full", "sdpa_sliding"])

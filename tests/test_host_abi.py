@@ -83,3 +83,17 @@ def test_no_gpu_fails_loudly(hb):
     with pytest.raises(hb.HydraCudaError) as info:
         hb.Context(0)
     assert "CUDA" in str(info.value)
+
+
+def test_shard_description_is_checked_before_any_device_is_touched(hb):
+    """hc_shard_create: an inconsistent (mode, rank, world), or a sequence shard over several ranks
+    without a communicator, is a communication error; both are decided on the host."""
+    for mode, rank, world in [(hb.capi.HC_SHARD_SEQUENCE, 3, 2), (hb.capi.HC_SHARD_SEQUENCE, -1, 2),
+                              (hb.capi.HC_SHARD_HEADS, 0, 0), (7, 0, 2)]:
+        with pytest.raises(hb.CommError) as info:
+            hb.Shard(None, mode, rank, world)
+        assert "inconsistent shard description" in str(info.value)
+    # a consistent description still needs a context
+    with pytest.raises(hb.HydraCudaError) as info:
+        hb.Shard(None, hb.capi.HC_SHARD_SEQUENCE, 1, 2)
+    assert info.value.status == hb.capi.HC_INVALID_ARGUMENT
