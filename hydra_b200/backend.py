@@ -494,6 +494,30 @@ class AttentionBackend:
         _check(self._lib.hc_layer_step(self.ctx.handle, cache.handle, layer, seq, _ptr(q), _ptr(k), _ptr(v),
                                        _ptr(out), tokens, first_position, ctypes.byref(s), _stream(stream)))
 
+    # A whole prompt in chunks, device buffers, one call (PrefillRunner's loop).
+    def prefill_chunks(self, cache: KVCache, layer: int, q, k, v, out, tokens: int, first_position: int,
+                       chunk: int, params: AttnParams, seq: int = 0, stream=None) -> None:
+        s = params.struct()
+        _check(self._lib.hc_prefill_chunks(self.ctx.handle, cache.handle, layer, seq, _ptr(q), _ptr(k), _ptr(v),
+                                           _ptr(out), tokens, first_position, chunk, ctypes.byref(s),
+                                           _stream(stream)))
+
+    # A whole prompt in chunks with host buffers: the copies overlap the kernels.
+    def prefill_host(self, cache: KVCache, layer: int, q, k, v, out, tokens: int, first_position: int,
+                     chunk: int, params: AttnParams, seq: int = 0, stream=None) -> None:
+        def host(a):
+            if a is None or isinstance(a, int):
+                return a
+            if hasattr(a, "ctypes"):
+                return int(a.ctypes.data)
+            return int(a.data_ptr())
+        s = params.struct()
+        if params.gate is not None:
+            s.gate = host(params.gate)
+        _check(self._lib.hc_prefill_host(self.ctx.handle, cache.handle, layer, seq, host(q), host(k), host(v),
+                                         host(out), tokens, first_position, chunk, ctypes.byref(s),
+                                         _stream(stream)))
+
     # One whole step with host buffers (numpy arrays or raw addresses).
     def layer_step_host(self, cache: KVCache, layer: int, q, k, v, out, tokens: int,
                         first_position: int, params: AttnParams, seq: int = 0, stream=None) -> None:

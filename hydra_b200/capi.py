@@ -105,6 +105,10 @@ _PROTOTYPES = {
     "hc_qwen_apply_output_gate": (c_int, [_P, _P, _P, c_size_t, c_int, _P]),
     "hc_layer_step": (c_int, [_P, _P, c_int, c_int, _P, _P, _P, _P, c_int, c_int,
                               POINTER(AttnParamsStruct), _P]),
+    "hc_prefill_chunks": (c_int, [_P, _P, c_int, c_int, _P, _P, _P, _P, c_int, c_int, c_int,
+                                  POINTER(AttnParamsStruct), _P]),
+    "hc_prefill_host": (c_int, [_P, _P, c_int, c_int, _P, _P, _P, _P, c_int, c_int, c_int,
+                                POINTER(AttnParamsStruct), _P]),
     "hc_layer_step_host": (c_int, [_P, _P, c_int, c_int, _P, _P, _P, _P, c_int, c_int,
                                    POINTER(AttnParamsStruct), _P]),
 }

@@ -628,9 +628,18 @@ hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n
         err = cudaMalloc(&ws.qprep, size_t(ws.qprep_tokens) * max_q_elems * 2);
         if (err == cudaSuccess) err = cudaMalloc(&ws.part_o, part_o_floats * sizeof(float));
         if (err == cudaSuccess) err = cudaMalloc(&ws.part_ml, part_ml_floats * sizeof(float));
-        // Staging for hc_layer_step_host: q (twice as wide when the gate is interleaved), gate, out, k, v.
-        cache->stage_bytes = size_t(ws.qprep_tokens) * (4 * max_q_elems + 2 * max_kv_elems) * 4;
-        if (err == cudaSuccess) err = cudaMalloc(&cache->stage_dev, cache->stage_bytes);
+        // Staging for the host-buffer entry points, two slots: q (twice as wide when the gate is
+        // interleaved), gate, out, k, v.
+        cache->stage_bytes = (size_t(ws.qprep_tokens) * (4 * max_q_elems + 2 * max_kv_elems) * 4 + 1023) & ~size_t(1023);
+        if (err == cudaSuccess) err = cudaMalloc(&cache->stage_dev, 2 * cache->stage_bytes);
+        if (err == cudaSuccess) err = cudaStreamCreateWithFlags(&cache->copy_in, cudaStreamNonBlocking);
+        if (err == cudaSuccess) err = cudaStreamCreateWithFlags(&cache->copy_out, cudaStreamNonBlocking);
+        for (int i = 0; i < 2 && err == cudaSuccess; ++i) {
+            err = cudaEventCreateWithFlags(&cache->in_done[i], cudaEventDisableTiming);
+            if (err == cudaSuccess) err = cudaEventCreateWithFlags(&cache->step_done[i], cudaEventDisableTiming);
+            if (err == cudaSuccess) err = cudaEventCreateWithFlags(&cache->out_done[i], cudaEventDisableTiming);
+        }
+        if (err == cudaSuccess) err = cudaEventCreateWithFlags(&cache->entry, cudaEventDisableTiming);
         if (err != cudaSuccess) {
             cudaGetLastError();
             st = fail(HC_ALLOC_FAILED, std::string("KV cache workspace: ") + cudaGetErrorString(err));
@@ -657,6 +666,14 @@ void hc_kv_cache_destroy(hc_kv_cache* cache) {
     if (cache->ws.part_o) cudaFree(cache->ws.part_o);
     if (cache->ws.part_ml) cudaFree(cache->ws.part_ml);
     if (cache->stage_dev) cudaFree(cache->stage_dev);
+    if (cache->copy_in) cudaStreamDestroy(cache->copy_in);
+    if (cache->copy_out) cudaStreamDestroy(cache->copy_out);
+    for (int i = 0; i < 2; ++i) {
+        if (cache->in_done[i]) cudaEventDestroy(cache->in_done[i]);
+        if (cache->step_done[i]) cudaEventDestroy(cache->step_done[i]);
+        if (cache->out_done[i]) cudaEventDestroy(cache->out_done[i]);
+    }
+    if (cache->entry) cudaEventDestroy(cache->entry);
     delete cache;
 }
 
@@ -1024,6 +1041,95 @@ hc_status hc_layer_step(hc_context* ctx, hc_kv_cache* cache, int layer, int seq,
     return hc_attention_prefill(ctx, cache, layer, seq, q, out, tokens, first_position, params, stream);
 }
 
+hc_status hc_prefill_chunks(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q, const void* k,
+                            const void* v, void* out, int tokens, int first_position, int chunk,
+                            const hc_attn_params* params, void* stream) {
+    if (!ctx || !q || !k || !v || !out) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    hc_status st = validate_params(cache, layer, params);
+    if (st != HC_OK) return st;
+    if (tokens <= 0 || chunk <= 0) return fail(HC_INVALID_ARGUMENT, "tokens and chunk must be positive");
+    const int d = params->head_dim;
+    const int mult = params->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
+    for (int start = 0; start < tokens; start += chunk) {
+        const int count = std::min(chunk, tokens - start);
+        hc_attn_params local = *params;
+        if (params->gate_layout == HC_GATE_SEPARATE) {
+            local.gate = offset_rows(params->gate, size_t(start), size_t(params->q_heads) * d, params->io_dtype);
+        }
+        st = hc_layer_step(ctx, cache, layer, seq,
+                           offset_rows(q, size_t(start), size_t(params->q_heads) * d * mult, params->io_dtype),
+                           offset_rows(k, size_t(start), size_t(params->kv_heads) * d, params->io_dtype),
+                           offset_rows(v, size_t(start), size_t(params->kv_heads) * d, params->io_dtype),
+                           const_cast<unsigned char*>(offset_rows(out, size_t(start), size_t(params->q_heads) * d, params->io_dtype)),
+                           count, first_position + start, &local, stream);
+        if (st != HC_OK) return st;
+    }
+    return HC_OK;
+}
+
+// The body of the host-buffer entry points.  Chunk i's inputs are copied in on one stream while chunk
+// i - 1 runs on the caller's stream and chunk i - 2's output is copied back on a third; two staging
+// slots, ordered by events.  One cudaMemcpyAsync per buffer.
+static hc_status host_chunks(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q, const void* k,
+                             const void* v, void* out, int tokens, int first_position, int chunk,
+                             const hc_attn_params* params, cudaStream_t s) {
+    const size_t eb = dtype_bytes(params->io_dtype);
+    const int d = params->head_dim;
+    const int mult = params->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
+    const bool sep_gate = params->gate_layout == HC_GATE_SEPARATE;
+    const size_t q_row = size_t(params->q_heads) * d * mult * eb;
+    const size_t kv_row = size_t(params->kv_heads) * d * eb;
+    const size_t o_row = size_t(params->q_heads) * d * eb;
+    auto align = [](size_t x) { return (x + 255) & ~size_t(255); };
+    const size_t off_k = align(q_row * chunk);
+    const size_t off_v = off_k + align(kv_row * chunk);
+    const size_t off_g = off_v + align(kv_row * chunk);
+    const size_t off_o = off_g + (sep_gate ? align(o_row * chunk) : 0);
+    if (off_o + o_row * chunk > cache->stage_bytes) return fail(HC_KV_OVERFLOW, "staging buffer too small for this chunk");
+    // The copies may start once the work already in the caller's stream has been reached.
+    cudaError_t err = cudaEventRecord(cache->entry, s);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(cache->copy_in, cache->entry, 0);
+    if (err != cudaSuccess) return check_cuda(err, "host step: entry event");
+    const unsigned char* hq = static_cast<const unsigned char*>(q);
+    const unsigned char* hk = static_cast<const unsigned char*>(k);
+    const unsigned char* hv = static_cast<const unsigned char*>(v);
+    const unsigned char* hg = static_cast<const unsigned char*>(params->gate);
+    unsigned char* ho = static_cast<unsigned char*>(out);
+    int index = 0;
+    for (int start = 0; start < tokens; start += chunk, ++index) {
+        const int count = std::min(chunk, tokens - start);
+        const int slot = index & 1;
+        unsigned char* base = static_cast<unsigned char*>(cache->stage_dev) + size_t(slot) * cache->stage_bytes;
+        // The slot's previous occupant (chunk index - 2) must have run and its output left.
+        if (index >= 2) {
+            err = cudaStreamWaitEvent(cache->copy_in, cache->out_done[slot], 0);
+            if (err != cudaSuccess) return check_cuda(err, "host step: slot reuse");
+        }
+        err = cudaMemcpyAsync(base, hq + size_t(start) * q_row, q_row * count, cudaMemcpyHostToDevice, cache->copy_in);
+        if (err == cudaSuccess) err = cudaMemcpyAsync(base + off_k, hk + size_t(start) * kv_row, kv_row * count, cudaMemcpyHostToDevice, cache->copy_in);
+        if (err == cudaSuccess) err = cudaMemcpyAsync(base + off_v, hv + size_t(start) * kv_row, kv_row * count, cudaMemcpyHostToDevice, cache->copy_in);
+        if (err == cudaSuccess && sep_gate) err = cudaMemcpyAsync(base + off_g, hg + size_t(start) * o_row, o_row * count, cudaMemcpyHostToDevice, cache->copy_in);
+        if (err == cudaSuccess) err = cudaEventRecord(cache->in_done[slot], cache->copy_in);
+        if (err == cudaSuccess) err = cudaStreamWaitEvent(s, cache->in_done[slot], 0);
+        if (err != cudaSuccess) return check_cuda(err, "host to device copy");
+        hc_attn_params local = *params;
+        if (sep_gate) local.gate = base + off_g;
+        const hc_status st = hc_layer_step(ctx, cache, layer, seq, base, base + off_k, base + off_v, base + off_o, count,
+                                           first_position + start, &local, s);
+        if (st != HC_OK) return st;
+        err = cudaEventRecord(cache->step_done[slot], s);
+        if (err == cudaSuccess) err = cudaStreamWaitEvent(cache->copy_out, cache->step_done[slot], 0);
+        if (err == cudaSuccess) err = cudaMemcpyAsync(ho + size_t(start) * o_row, base + off_o, o_row * count, cudaMemcpyDeviceToHost, cache->copy_out);
+        if (err == cudaSuccess) err = cudaEventRecord(cache->out_done[slot], cache->copy_out);
+        if (err != cudaSuccess) return check_cuda(err, "device to host copy");
+    }
+    // The call returns when the results are on the host.
+    err = cudaStreamSynchronize(cache->copy_out);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+    if (err != cudaSuccess) return check_cuda(err, "host step: synchronise");
+    return HC_OK;
+}
+
 hc_status hc_layer_step_host(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q, const void* k,
                              const void* v, void* out, int tokens, int first_position,
                              const hc_attn_params* params, void* stream) {
@@ -1034,35 +1140,22 @@ hc_status hc_layer_step_host(hc_context* ctx, hc_kv_cache* cache, int layer, int
     if (tokens > cache->ws.qprep_tokens) {
         return fail(HC_KV_OVERFLOW, "hc_layer_step_host takes at most " + std::to_string(cache->ws.qprep_tokens) + " tokens per call");
     }
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const size_t eb = dtype_bytes(params->io_dtype);
-    const int d = params->head_dim;
-    const int mult = params->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
-    const size_t q_bytes = size_t(tokens) * params->q_heads * d * mult * eb;
-    const size_t kv_bytes = size_t(tokens) * params->kv_heads * d * eb;
-    const size_t o_bytes = size_t(tokens) * params->q_heads * d * eb;
-    const bool sep_gate = params->gate_layout == HC_GATE_SEPARATE;
-    auto align = [](size_t x) { return (x + 255) & ~size_t(255); };
-    unsigned char* base = static_cast<unsigned char*>(cache->stage_dev);
-    unsigned char* dq = base;
-    unsigned char* dk = dq + align(q_bytes);
-    unsigned char* dv = dk + align(kv_bytes);
-    unsigned char* dg = dv + align(kv_bytes);
-    unsigned char* dout = dg + (sep_gate ? align(o_bytes) : 0);
-    if (size_t(dout - base) + o_bytes > cache->stage_bytes) return fail(HC_KV_OVERFLOW, "staging buffer too small");
-    cudaError_t err = cudaMemcpyAsync(dq, q, q_bytes, cudaMemcpyHostToDevice, s);
-    if (err == cudaSuccess) err = cudaMemcpyAsync(dk, k, kv_bytes, cudaMemcpyHostToDevice, s);
-    if (err == cudaSuccess) err = cudaMemcpyAsync(dv, v, kv_bytes, cudaMemcpyHostToDevice, s);
-    if (err == cudaSuccess && sep_gate) err = cudaMemcpyAsync(dg, params->gate, o_bytes, cudaMemcpyHostToDevice, s);
-    if (err != cudaSuccess) return check_cuda(err, "host to device copy");
-    hc_attn_params local = *params;
-    if (sep_gate) local.gate = dg;
-    st = hc_layer_step(ctx, cache, layer, seq, dq, dk, dv, dout, tokens, first_position, &local, stream);
+    return host_chunks(ctx, cache, layer, seq, q, k, v, out, tokens, first_position, tokens, params,
+                       static_cast<cudaStream_t>(stream));
+}
+
+hc_status hc_prefill_host(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q, const void* k,
+                          const void* v, void* out, int tokens, int first_position, int chunk,
+                          const hc_attn_params* params, void* stream) {
+    if (!ctx || !q || !k || !v || !out) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    hc_status st = validate_params(cache, layer, params);
     if (st != HC_OK) return st;
-    err = cudaMemcpyAsync(out, dout, o_bytes, cudaMemcpyDeviceToHost, s);
-    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
-    if (err != cudaSuccess) return check_cuda(err, "device to host copy");
-    return HC_OK;
+    if (tokens <= 0 || chunk <= 0) return fail(HC_INVALID_ARGUMENT, "tokens and chunk must be positive");
+    if (chunk > cache->ws.qprep_tokens) {
+        return fail(HC_KV_OVERFLOW, "hc_prefill_host takes chunks of at most " + std::to_string(cache->ws.qprep_tokens) + " tokens");
+    }
+    return host_chunks(ctx, cache, layer, seq, q, k, v, out, tokens, first_position, chunk, params,
+                       static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

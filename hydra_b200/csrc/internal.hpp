@@ -143,9 +143,16 @@ struct hc_kv_cache {
     hc_shard_desc shard{HC_SHARD_NONE, 0, 1};
     std::vector<int> lengths;
     hc::Workspace ws;
-    void* stage_host = nullptr;   // pinned, for hc_layer_step_host
+    // hc_layer_step_host / hc_prefill_host: two device staging slots, a stream for the copies in and
+    // one for the copies out, and the events that order them against the caller's stream.
     void* stage_dev = nullptr;
-    size_t stage_bytes = 0;
+    size_t stage_bytes = 0;       // of one slot
+    cudaStream_t copy_in = nullptr;
+    cudaStream_t copy_out = nullptr;
+    cudaEvent_t in_done[2] = {nullptr, nullptr};
+    cudaEvent_t step_done[2] = {nullptr, nullptr};
+    cudaEvent_t out_done[2] = {nullptr, nullptr};
+    cudaEvent_t entry = nullptr;
 };
 
 namespace hc {

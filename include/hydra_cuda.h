@@ -387,6 +387,15 @@ HC_API hc_status hc_layer_step(hc_context* ctx, hc_kv_cache* cache, int layer, i
                                const void* q, const void* k, const void* v, void* out, int tokens,
                                int first_position, const hc_attn_params* params, void* stream);
 
+/* hc_layer_step for a whole prompt: `tokens` tokens in chunks of `chunk` (the reference's
+ * PrefillRunner loop, Sources/HydraMetal/PrefillRunner.swift:128-184, one call per prompt instead of
+ * one per chunk).  Each chunk is one hc_layer_step, enqueued in order on `stream`; the results are
+ * bit for bit those of the chunk-by-chunk calls. */
+HC_API hc_status hc_prefill_chunks(hc_context* ctx, hc_kv_cache* cache, int layer, int seq,
+                                   const void* q, const void* k, const void* v, void* out,
+                                   int tokens, int first_position, int chunk,
+                                   const hc_attn_params* params, void* stream);
+
 /* ---- host-buffer convenience (what a runner without device buffers of its own calls) --------- */
 
 /* One whole step of the path with HOST buffers: copies q, k, v (and gate) to the device, appends,
@@ -400,6 +409,15 @@ HC_API hc_status hc_layer_step_host(hc_context* ctx, hc_kv_cache* cache, int lay
                                     const void* q, const void* k, const void* v, void* out,
                                     int tokens, int first_position, const hc_attn_params* params,
                                     void* stream);
+
+/* The same for a whole prompt in chunks of `chunk` tokens (at most max(prefill_chunk, max_seqs)): the
+ * copy in of chunk i + 1 and the copy out of chunk i - 1 run under the kernels of chunk i (two
+ * staging slots, the library's own copy streams, events), and the call returns when every result is
+ * on the host.  Use pinned host memory, or the copies serialise. */
+HC_API hc_status hc_prefill_host(hc_context* ctx, hc_kv_cache* cache, int layer, int seq,
+                                 const void* q, const void* k, const void* v, void* out,
+                                 int tokens, int first_position, int chunk,
+                                 const hc_attn_params* params, void* stream);
 
 #ifdef __cplusplus
 }

@@ -434,6 +434,56 @@ def test_layer_step_with_host_buffers(hb, ctx):
     layer.close()
 
 
+@pytest.mark.parametrize("gated", [False, True])
+def test_whole_prompt_entry_points_equal_the_chunk_by_chunk_calls(hb, ctx, gated):
+    """hc_prefill_chunks (device buffers) and hc_prefill_host (pinned host buffers, copies overlapped
+    with the kernels over two staging slots) against one hc_layer_step per chunk: the same bits, with a
+    last chunk that is not full and more chunks than staging slots."""
+    import torch
+    rng = np.random.default_rng(171)
+    qh, kvh, d, tokens, chunk = 16, 4, 64, 1100, 256
+    q = tl.normal_bf16(rng, (tokens, qh, d))
+    k = tl.normal_bf16(rng, (tokens, kvh, d))
+    v = tl.normal_bf16(rng, (tokens, kvh, d))
+    gate = tl.normal_bf16(rng, (tokens, qh, d)) if gated else None
+    sinks = tl.normal_bf16(rng, (qh,))
+    inv = ho.inverse_frequencies(d, 10000.0)
+    outs = {}
+    for mode in ("steps", "chunks", "host"):
+        layer = tl.Layer(hb, ctx, qh, kvh, d, 2048, sinks=sinks, rope_inv_freq=inv, prefill_chunk=chunk)
+        dev = {name: tl.to_device(x) for name, x in (("q", q), ("k", k), ("v", v))}
+        params = layer.params
+        gate_dev = tl.to_device(gate) if gated else None
+        if gated:
+            params = layer._with_gate(gate_dev)
+        out = tl.device_empty((tokens, qh, d))
+        if mode == "steps":
+            for start in range(0, tokens, chunk):
+                n = min(chunk, tokens - start)
+                p = layer._with_gate(gate_dev[start:]) if gated else params
+                layer.backend.layer_step(layer.cache, 0, dev["q"][start:], dev["k"][start:], dev["v"][start:],
+                                         out[start:], n, start, p)
+        elif mode == "chunks":
+            layer.backend.prefill_chunks(layer.cache, 0, dev["q"], dev["k"], dev["v"], out, tokens, 0, chunk, params)
+        else:
+            host = {name: t.cpu().pin_memory() for name, t in dev.items()}
+            host_out = torch.zeros((tokens, qh, d), dtype=torch.bfloat16).pin_memory()
+            p = params
+            if gated:
+                import dataclasses
+                host_gate = gate_dev.cpu().pin_memory()
+                p = dataclasses.replace(params, gate=host_gate)
+            layer.backend.prefill_host(layer.cache, 0, host["q"], host["k"], host["v"], host_out, tokens, 0, chunk, p)
+            out = host_out
+        ctx.check()
+        outs[mode] = tl.to_host(out) if mode != "host" else out.float().numpy()
+        layer.close()
+    assert np.array_equal(outs["steps"], outs["chunks"])
+    assert np.array_equal(outs["steps"], outs["host"])
+    want = tl.oracle_path(q, k, v, np.arange(tokens), 0.125, 0, sinks=sinks, gate=gate, inv_freq=inv)
+    assert tl.within_tolerance(outs["steps"], want)
+
+
 @pytest.mark.parametrize("d,window", [(64, 0), (128, 96), (256, 0), (96, 0)])
 def test_layer_step_equals_append_then_attention(hb, ctx, d, window):
     """hc_layer_step (one prologue launch for k, v and q) gives bit for bit what hc_kv_append followed
