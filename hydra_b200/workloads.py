@@ -185,13 +185,14 @@ class PathRunner:
     """Owns the cache, tables and device tensors of one configuration and runs its passes."""
 
     def __init__(self, ctx: Context, cfg: Config, inputs: Inputs, kernel_path: int = capi.HC_PATH_AUTO,
-                 shard: Optional[tuple] = None):
+                 shard: Optional[tuple] = None, storage: int = capi.HC_STORAGE_AUTO):
         import torch
         self.torch = torch
         self.ctx, self.cfg, self.inputs = ctx, cfg, inputs
         self.backend = AttentionBackend(ctx)
         d = cfg.head_dim
-        descs = [dict(q_heads=cfg.q_heads, kv_heads=cfg.kv_heads, head_dim=d, window=l.window) for l in cfg.layers]
+        descs = [dict(q_heads=cfg.q_heads, kv_heads=cfg.kv_heads, head_dim=d, window=l.window, storage=storage)
+                 for l in cfg.layers]
         self.cache = KVCache(ctx, descs, cfg.context, prefill_chunk=max(cfg.chunk, 1), max_seqs=cfg.batch, shard=shard)
         self.tables, self.params, self.dev = [], [], []
         bf = torch.bfloat16

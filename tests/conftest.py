@@ -28,3 +28,17 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """The raw max-abs error and the reference-style deviation (max |a - e| / max |e|,
+    Tests/HydraMetalTests/AttentionKernelTests.swift:29-37) of every full-size parity case."""
+    try:
+        from tests import hydra_testlib as tl
+    except Exception:
+        return
+    if not tl.MARGINS:
+        return
+    terminalreporter.write_line("parity margins against the oracle (bound: max-abs 1e-2):")
+    for name, worst, dev, count in tl.MARGINS:
+        terminalreporter.write_line(f"  {name}: max-abs {worst:.3e}, deviation {dev:.3e} over {count} values")
