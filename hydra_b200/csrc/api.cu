@@ -71,6 +71,7 @@ CacheView view_of(const hc_kv_cache* cache, const hc_layer_store& L) {
     const bool sequence = cache->shard.mode == HC_SHARD_SEQUENCE && cache->shard.world > 1;
     view.map.rank = sequence ? cache->shard.rank : 0;
     view.map.world = sequence ? cache->shard.world : 1;
+    view.map.log_segment = L.log_segment;
     return view;
 }
 
@@ -248,7 +249,7 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
             ep.gate = q_rows;
         }
         if (tensor) {
-            st = tc_prefill(ctx, shape, L, view, seq, q_bf16, count, first_position + start, ep, stream);
+            st = tc_prefill(ctx, shape, L, view, seq, q_bf16, count, first_position + start, cache->ws, ep, stream);
         } else {
             st = simt_prefill(ctx, shape, view, seq, q_bf16, count, first_position + start, ep, stream);
         }
@@ -611,12 +612,38 @@ hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n
         }
         max_q_elems = std::max(max_q_elems, size_t(L.desc.q_heads) * d);
         max_kv_elems = std::max(max_kv_elems, size_t(L.desc.kv_heads) * d);
-        // Split-attention workspace: one partial per (sequence of a launch, query head, visible tile).
-        int visible_tiles = windowed ? L.desc.window / kTileKeys + 2 : (context_length + kTileKeys - 1) / kTileKeys;
-        if (sequence) visible_tiles = (visible_tiles + sd.world - 1) / sd.world + 1;
-        const size_t rows = size_t(std::min(max_seqs, kMaxBatch)) * L.desc.q_heads;
-        part_o_floats = std::max(part_o_floats, rows * visible_tiles * d);
-        part_ml_floats = std::max(part_ml_floats, rows * visible_tiles * 2);
+        // How the layer groups its key tiles (see common.cuh): short segments where launches gain from
+        // cutting their rows' keys at little cost in partials, long ones elsewhere.
+        //   prefill: when even a full chunk gives too few (row tile, kv head) pairs to occupy the SMs
+        //            (half of them; a quarter for head_dim 256, whose kernel pays more per item) and a
+        //            row can span more than two short segments;
+        //   decode:  a cache for batches of sequences, whose split kernel then leaves one partial per
+        //            1024 keys instead of one per 128.
+        const int tokens_per_tile = kTileKeys / (L.desc.q_heads / L.desc.kv_heads);
+        const int chunk_row_tiles = (prefill_chunk + tokens_per_tile - 1) / tokens_per_tile;
+        const int reach = windowed ? std::min(L.desc.window + prefill_chunk, context_length) : context_length;
+        const bool few_rows = (d == 256 ? 4 : 2) * chunk_row_tiles * L.desc.kv_heads <= std::max(ctx->sm_count, 1) &&
+                              reach > (2 * kTileKeys << kLogSegmentSmall);
+        const bool batched = max_seqs >= 8;
+        L.log_segment = few_rows || batched ? kLogSegmentSmall : kLogSegmentLarge;
+        // Workspace for the partials of split launches.  Decode, at its finest cut: one per (batch
+        // entry, query head, key tile of this rank).  Prefill, layers with short segments only: one
+        // per (query token, query head, segment).
+        const int world = sequence ? sd.world : 1;
+        const int decode_reach = windowed ? std::min(L.desc.window + kTileKeys, context_length) : context_length;
+        const size_t decode_slots = size_t(((decode_reach + kTileKeys - 1) / kTileKeys + world - 1) / world + 1);
+        const size_t decode_rows = size_t(std::min(max_seqs, kMaxBatch)) * L.desc.q_heads;
+        part_o_floats = std::max(part_o_floats, decode_rows * decode_slots * d);
+        part_ml_floats = std::max(part_ml_floats, decode_rows * decode_slots * 2);
+        if (few_rows) {
+            const size_t prefill_slots = size_t((((reach + kTileKeys - 1) / kTileKeys) >> kLogSegmentSmall) + 2);
+            const size_t prefill_rows = size_t(prefill_chunk) * L.desc.q_heads;
+            part_o_floats = std::max(part_o_floats, prefill_rows * prefill_slots * d);
+            part_ml_floats = std::max(part_ml_floats, prefill_rows * prefill_slots * 2);
+        }
+        // The tensor-core kernels keep a whole-row launch's second-fold state in the same buffer:
+        // head_dim x 128 floats per thread block.
+        if (d == 64 || d == 128 || d == 256) part_o_floats = std::max(part_o_floats, size_t(std::max(ctx->sm_count, 1)) * d * 128);
         st = tc_make_tensor_maps(cache, L);
     }
     if (st == HC_OK && max_q_elems == 0) st = fail(HC_UNSUPPORTED, "no layer keeps a key/value history");

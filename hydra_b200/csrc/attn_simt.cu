@@ -1,9 +1,13 @@
 // attn_simt.cu — the CUDA-core attention kernels: any head_dim up to 512, any group size up to 16.
 //
-// Three kernels share one tile-partial routine (see common.cuh for the canonical computation):
-//   decode_tiles_kernel   one CTA per (key tile, kv head, sequence): writes the tile's partial
-//   merge_tiles_kernel    one CTA per (query head, sequence): folds the partials in tile order
-//   prefill_rows_kernel   one CTA per (kv head, token): walks the token's tiles and folds in place
+// The kernels share one tile-partial routine (see common.cuh for the canonical computation):
+//   decode_runs_kernel    one CTA per (run of key tiles, kv head, sequence): writes the run's tile
+//                         partials, or the partial of a whole segment
+//   merge_decode_kernel   one CTA per (query head, batch entry): the folds the split kernel left,
+//                         then the epilogue (also finishes the decode rows of the tcgen05 kernels)
+//   merge_rows_kernel     a warp per (query token, head): the second fold over the segment partials
+//                         of a prefill chunk that the tcgen05 kernels split
+//   prefill_rows_kernel   one CTA per (kv head, token): both folds in place
 //
 // decode = split over key tiles + merge replaces attention_decode / attention_decode_split /
 // attention_decode_merge (Sources/HydraMetal/Shaders/attention.metal:132-242, 307-452).
@@ -38,20 +42,25 @@ struct SimtSmem {
     uint16_t* kv;    // [32][d + 8] staged K or V rows
 };
 
-__host__ __device__ inline size_t simt_smem_bytes(int G, int d, bool with_state) {
+struct FoldState {
+    float* A;        // [G][d]
+    float* M;        // [G]
+    float* L;        // [G]
+};
+
+__host__ __device__ inline size_t simt_smem_bytes(int G, int d, int states) {
     size_t floats = size_t(G) * d          // q
                   + size_t(G) * kTileKeys  // s
                   + size_t(G) * d          // acc
                   + 2 * size_t(G);         // mm, l
-    if (with_state) floats += size_t(G) * d + 2 * size_t(G);   // A, M, L
+    floats += size_t(states) * (size_t(G) * d + 2 * size_t(G));   // A, M, L of each fold state
     size_t bytes = floats * 4;
     bytes = (bytes + 15) & ~size_t(15);
     bytes += size_t(kSubKeys) * (d + kRowPad) * 2;
     return bytes;
 }
 
-__device__ inline SimtSmem carve(unsigned char* raw, int G, int d, bool with_state, float** A,
-                                 float** M, float** L) {
+__device__ inline SimtSmem carve(unsigned char* raw, int G, int d, int states, FoldState* state) {
     SimtSmem sm;
     float* f = reinterpret_cast<float*>(raw);
     sm.q = f;            f += size_t(G) * d;
@@ -59,10 +68,10 @@ __device__ inline SimtSmem carve(unsigned char* raw, int G, int d, bool with_sta
     sm.acc = f;          f += size_t(G) * d;
     sm.mm = f;           f += G;
     sm.l = f;            f += G;
-    if (with_state) {
-        *A = f;          f += size_t(G) * d;
-        *M = f;          f += G;
-        *L = f;          f += G;
+    for (int i = 0; i < states; ++i) {
+        state[i].A = f;  f += size_t(G) * d;
+        state[i].M = f;  f += G;
+        state[i].L = f;  f += G;
     }
     size_t offset = size_t(reinterpret_cast<unsigned char*>(f) - raw);
     offset = (offset + 15) & ~size_t(15);
@@ -220,91 +229,126 @@ __device__ inline void write_result(const EpilogueArgs& ep, size_t row, int q_he
     store_io(ep.out, (row * q_heads + head) * d + i, ep.io_dtype, finish_value(A, L, gated, g));
 }
 
-// First and last absolute tile a query at `position` touches, restricted to tiles this rank owns.
-__device__ __host__ inline void tile_span(int position, int window, int& lo, int& first_tile,
-                                          int& last_tile) {
-    lo = window > 0 ? max(0, position - window + 1) : 0;
-    first_tile = lo / kTileKeys;
-    last_tile = position / kTileKeys;
+// ---- the first fold: one segment's tiles into a fold state ---------------------------------------
+// Runs tile_partial over the segment's tiles (ascending, `world` apart) and folds each into `st`,
+// which starts empty.  Queries of the G heads are in sm.q; [lo, hi] are the visible positions.
+__device__ void segment_partial(const SimtSmem& sm, const FoldState& st, const CacheView& cache, size_t head_rows,
+                                const TileRange& tiles, int lo, int hi, int G, int d, float c) {
+    for (int i = threadIdx.x; i < G * d; i += kThreads) st.A[i] = 0.0f;
+    if (threadIdx.x < G) {
+        st.M[threadIdx.x] = kEmptyMax;
+        st.L[threadIdx.x] = 0.0f;
+    }
+    __syncthreads();
+    const int world = max(cache.map.world, 1);
+    for (int j = 0; j < tiles.count; ++j) {
+        const int tile = tiles.first + j * world;
+        const size_t row0 = head_rows + row_of_tile(cache.map, tile);
+        tile_partial(sm, cache.k + row0 * d, cache.v + row0 * d, tile * kTileKeys, lo, hi, G, d, c);
+        for (int i = threadIdx.x; i < G * d; i += kThreads) {
+            const int g = i / d;
+            float Mn, a, b;
+            fold_coefficients(st.M[g], sm.mm[g], Mn, a, b);
+            st.A[i] = fold_value(st.A[i], a, sm.acc[i], b);
+        }
+        __syncthreads();
+        if (threadIdx.x < G) {
+            const int g = threadIdx.x;
+            float Mn, a, b;
+            fold_coefficients(st.M[g], sm.mm[g], Mn, a, b);
+            st.L[g] = __fmaf_rn(st.L[g], a, __fmul_rn(sm.l[g], b));
+            st.M[g] = Mn;
+        }
+        __syncthreads();
+    }
 }
 
-// ---- decode: one tile per CTA -----------------------------------------------------------------
+// ---- decode: one run of key tiles per CTA, its partial(s) to the workspace ---------------------------
+// With tile_partials the run's tiles each leave their own partial (slot = ordinal of the tile among the
+// row's tiles on this rank); otherwise the run is a whole segment and leaves the segment's partial
+// (slot = ordinal of the segment).
 __global__ void __launch_bounds__(kThreads)
-decode_tiles_kernel(const AttnShape shape, const CacheView cache, const BatchMeta meta,
-                    const uint16_t* __restrict__ q, float* __restrict__ part_o,
-                    float* __restrict__ part_ml, int part_tiles) {
+decode_runs_kernel(const AttnShape shape, const CacheView cache, const BatchMeta meta,
+                   const uint16_t* __restrict__ q, float* __restrict__ part_o,
+                   float* __restrict__ part_ml, int slots, int log_run, int tile_partials) {
     extern __shared__ __align__(16) unsigned char raw[];
     const int G = shape.group, d = shape.head_dim;
     const int kv_head = blockIdx.y;
     const int b = blockIdx.z;
     const int position = meta.pos[b];
-    int lo, first_tile, last_tile;
-    tile_span(position, shape.window, lo, first_tile, last_tile);
-    // Local tiles: with a sequence-sharded cache this rank owns tiles congruent to rank mod world.
-    const int world = max(cache.map.world, 1);
-    int tile = first_tile + blockIdx.x;
-    if (world > 1) {
-        const int first_owned = first_tile + ((cache.map.rank - first_tile % world) + world) % world;
-        tile = first_owned + blockIdx.x * world;
-    }
-    if (tile > last_tile) return;
+    const TileRange tiles = group_tiles(cache.map, position, position, shape.window, blockIdx.x, log_run);
+    if (tiles.count <= 0) return;
+    const int lo = shape.window > 0 ? max(0, position - shape.window + 1) : 0;
 
-    SimtSmem sm = carve(raw, G, d, false, nullptr, nullptr, nullptr);
+    FoldState st;
+    SimtSmem sm = carve(raw, G, d, 1, &st);
     load_group_queries(sm, q + (size_t(b) * shape.q_heads + size_t(kv_head) * G) * d, G, d);
     const size_t head_rows = (size_t(meta.seq[b]) * cache.kv_heads + kv_head) * cache.capacity;
-    const size_t row0 = head_rows + row_of_tile(cache.map, tile);
-    tile_partial(sm, cache.k + row0 * d, cache.v + row0 * d, tile * kTileKeys, lo, position, G, d,
-                 shape.c);
-
+    const size_t row0 = size_t(b) * shape.q_heads + size_t(kv_head) * G;
+    if (tile_partials) {
+        const int world = max(cache.map.world, 1);
+        const int slot0 = (tiles.first - row_tiles(cache.map, position, position, shape.window).first) / world;
+        __syncthreads();
+        for (int j = 0; j < tiles.count; ++j) {
+            const int tile = tiles.first + j * world;
+            const size_t krow = head_rows + row_of_tile(cache.map, tile);
+            tile_partial(sm, cache.k + krow * d, cache.v + krow * d, tile * kTileKeys, lo, position, G, d, shape.c);
+            for (int i = threadIdx.x; i < G * d; i += kThreads) {
+                const int g = i / d;
+                part_o[((row0 + g) * slots + slot0 + j) * d + (i - g * d)] = sm.acc[i];
+            }
+            if (threadIdx.x < G) {
+                part_ml[((row0 + threadIdx.x) * slots + slot0 + j) * 2] = sm.mm[threadIdx.x];
+                part_ml[((row0 + threadIdx.x) * slots + slot0 + j) * 2 + 1] = sm.l[threadIdx.x];
+            }
+            __syncthreads();
+        }
+        return;
+    }
+    segment_partial(sm, st, cache, head_rows, tiles, lo, position, G, d, shape.c);
+    const int slot = blockIdx.x;
     for (int i = threadIdx.x; i < G * d; i += kThreads) {
         const int g = i / d;
-        const size_t row = size_t(b) * shape.q_heads + size_t(kv_head) * G + g;
-        part_o[(row * part_tiles + blockIdx.x) * d + (i - g * d)] = sm.acc[i];
+        part_o[((row0 + g) * slots + slot) * d + (i - g * d)] = st.A[i];
     }
     if (threadIdx.x < G) {
-        const size_t row = size_t(b) * shape.q_heads + size_t(kv_head) * G + threadIdx.x;
-        part_ml[(row * part_tiles + blockIdx.x) * 2] = sm.mm[threadIdx.x];
-        part_ml[(row * part_tiles + blockIdx.x) * 2 + 1] = sm.l[threadIdx.x];
+        part_ml[((row0 + threadIdx.x) * slots + slot) * 2] = st.M[threadIdx.x];
+        part_ml[((row0 + threadIdx.x) * slots + slot) * 2 + 1] = st.L[threadIdx.x];
     }
 }
 
-// ---- merge: the fold over a row's tile partials ------------------------------------------------
-// The running maximum is a prefix maximum (exact under any association), so the coefficients of
-// every step are computed in parallel and only `acc = fma(acc, a, part * b)` stays sequential.
-constexpr int kMergeChunk = 1024;            // tiles folded per pass, at most (8 per thread)
+// ---- merge for decode rows: both folds over tile partials, or the second over segment partials -------
+// One block per (query head, batch entry).  The row's segments are taken sixteen at a time: the
+// block's warps first bring each segment's partial into shared memory (folding the segment's tile
+// partials, lane l holding columns l, l + 32, ..; or just copying a segment partial), which is where
+// a long row's work runs in parallel; then every thread runs the second fold for its columns.
+constexpr int kMergeThreads = 256;
+constexpr int kMergeSegments = 16;
 
-// COLS = columns of the row per thread: the block has min(128, head_dim) threads (64 for
-// head_dim <= 64), so no thread idles, and the fewer columns a thread carries the further ahead of
-// its dependent chain it fetches the partials (256 / 8 / COLS ... tiles in flight).
-template <int COLS>
-__global__ void __launch_bounds__(kThreads)
-merge_tiles_kernel(const AttnShape shape, const BatchMeta meta, const float* __restrict__ part_o,
-                   const float* __restrict__ part_ml, int part_tiles, int world, int rank,
-                   const EpilogueArgs ep) {
-    __shared__ float coef_a[kMergeChunk];
-    __shared__ float coef_b[kMergeChunk];
-    __shared__ float part_l[kMergeChunk];
-    __shared__ float warp_max[4];
-    const int threads = blockDim.x;              // 64 or 128
-    const int warps = threads >> 5;
-    const int chunk_tiles = threads * 8;
+__host__ __device__ inline size_t merge_smem_bytes(int d) { return size_t(kMergeSegments) * (d + 2) * sizeof(float); }
+
+template <int KCOLS>
+__global__ void __launch_bounds__(kMergeThreads)
+merge_decode_kernel(const AttnShape shape, const RowMap map, const BatchMeta meta, const float* __restrict__ part_o,
+                    const float* __restrict__ part_ml, int slots, int tile_partials, const EpilogueArgs ep) {
+    extern __shared__ __align__(16) unsigned char raw[];
     pdl_launch_dependents();
     pdl_wait();
     const int head = blockIdx.x;
-    const int b = blockIdx.y;
+    const int r = blockIdx.y;
     const int d = shape.head_dim;
+    float* seg_o = reinterpret_cast<float*>(raw);                 // [16][d]
+    float* seg_ml = seg_o + size_t(kMergeSegments) * d;           // [16][2]; M = -inf marks "nothing here"
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int position = meta.pos[b];
-    int lo, first_tile, last_tile;
-    tile_span(position, shape.window, lo, first_tile, last_tile);
-    int n_tiles;
-    if (world > 1) {
-        const int first_owned = first_tile + ((rank - first_tile % world) + world) % world;
-        n_tiles = first_owned > last_tile ? 0 : (last_tile - first_owned) / world + 1;
-    } else {
-        n_tiles = last_tile - first_tile + 1;
-    }
-    const size_t row = size_t(b) * shape.q_heads + head;
+    const int pos = meta.pos[r];
+    const int world = max(map.world, 1);
+    const int ls = map.log_segment;
+    const int tile_lo = first_visible_tile(pos, shape.window), tile_hi = pos / kTileKeys;
+    const int first_owned = row_tiles(map, pos, pos, shape.window).first;
+    const int n_segments = visible_groups(pos, pos, shape.window, ls);
+    const int segment0 = tile_lo >> ls;
+    const size_t row = size_t(r) * shape.q_heads + head;
+    const float neg_inf = __int_as_float(0xff800000);
 
     float M, L;
     if (shape.count_sink) {
@@ -315,90 +359,199 @@ merge_tiles_kernel(const AttnShape shape, const BatchMeta meta, const float* __r
         M = kEmptyMax;
         L = 0.0f;
     }
-    constexpr int kCols = COLS;
-    float A[kCols];
-    #pragma unroll
-    for (int cidx = 0; cidx < kCols; ++cidx) A[cidx] = 0.0f;
+    float A[2] = {0.0f, 0.0f};                                    // columns tid and tid + 256
 
-    for (int base = 0; base < n_tiles; base += chunk_tiles) {
-        const int count = min(chunk_tiles, n_tiles - base);
+    for (int base = 0; base < n_segments; base += kMergeSegments) {
+        const int count = min(kMergeSegments, n_segments - base);
         __syncthreads();
-        // Thread t owns 8 consecutive tiles: local inclusive prefix maximum, then a block scan.
-        float local[8];
-        float running = __int_as_float(0xff800000);
-        #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int t = tid * 8 + u;
-            const float mm = t < count ? part_ml[(row * part_tiles + base + t) * 2]
-                                       : __int_as_float(0xff800000);
-            local[u] = mm;
-            running = fmaxf(running, mm);
-        }
-        float inclusive = running;
-        #pragma unroll
-        for (int offset = 1; offset < 32; offset <<= 1) {
-            const float other = __shfl_up_sync(0xffffffffu, inclusive, offset);
-            if (lane >= offset) inclusive = fmaxf(inclusive, other);
-        }
-        if (lane == 31) warp_max[warp] = inclusive;
-        __syncthreads();
-        float before = M;                        // maximum of everything before this thread's tiles
-        for (int w = 0; w < warp; ++w) before = fmaxf(before, warp_max[w]);
-        const float prev_lane = __shfl_up_sync(0xffffffffu, inclusive, 1);
-        if (lane > 0) before = fmaxf(before, prev_lane);
-        #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int t = tid * 8 + u;
-            if (t < count) {
-                float Mn, a, bcoef;
-                fold_coefficients(before, local[u], Mn, a, bcoef);
-                coef_a[t] = a;
-                coef_b[t] = bcoef;
-                part_l[t] = __fmul_rn(part_ml[(row * part_tiles + base + t) * 2 + 1], bcoef);
-                before = Mn;
-            }
-        }
-        float chunk_max = M;
-        for (int w = 0; w < warps; ++w) chunk_max = fmaxf(chunk_max, warp_max[w]);
-        __syncthreads();
-
-        // The sequential part.  Every thread carries L (same chain, same bits) and its columns.
-        const float* o_base = part_o + (row * part_tiles + base) * d;
-        // The partials are fetched well ahead of the dependent chain that consumes them.
-        constexpr int kAhead = 32 / COLS;
-        for (int t0 = 0; t0 < count; t0 += kAhead) {
-            float part[kAhead][kCols];
+        for (int sl = warp; sl < count; sl += kMergeThreads / 32) {
+            const int segment = segment0 + base + sl;
+            const int g0 = max(segment << ls, tile_lo), g1 = min((segment << ls) + (1 << ls) - 1, tile_hi);
+            const TileRange tiles = owned_tiles(map, g0, g1);
+            float m1 = neg_inf, l1 = 0.0f;
+            float a1[KCOLS];
             #pragma unroll
-            for (int u = 0; u < kAhead; ++u) {
+            for (int k = 0; k < KCOLS; ++k) a1[k] = 0.0f;
+            if (tiles.count > 0 && !tile_partials) {
+                const size_t slot = row * slots + base + sl;
+                m1 = __ldg(part_ml + slot * 2);
+                l1 = __ldg(part_ml + slot * 2 + 1);
                 #pragma unroll
-                for (int cidx = 0; cidx < kCols; ++cidx) {
-                    const int i = tid + cidx * threads;
-                    part[u][cidx] = (t0 + u < count && i < d) ? __ldg(o_base + size_t(t0 + u) * d + i) : 0.0f;
+                for (int k = 0; k < KCOLS; ++k) {
+                    const int col = lane + 32 * k;
+                    if (col < d) a1[k] = __ldg(part_o + slot * d + col);
                 }
-            }
-            #pragma unroll
-            for (int u = 0; u < kAhead; ++u) {
-                if (t0 + u < count) {
-                    const float a = coef_a[t0 + u], bcoef = coef_b[t0 + u];
-                    L = __fmaf_rn(L, a, part_l[t0 + u]);
+            } else if (tiles.count > 0) {
+                // The first fold: the segment's tile partials, ascending, from the empty state.
+                m1 = kEmptyMax;
+                const size_t slot0 = row * slots + (tiles.first - first_owned) / world;
+                constexpr int kAhead = KCOLS <= 4 ? 32 / KCOLS : KCOLS == 8 ? 8 : 4;
+                for (int j0 = 0; j0 < tiles.count; j0 += kAhead) {
+                    float part[kAhead][KCOLS];
+                    float2 ml[kAhead];
                     #pragma unroll
-                    for (int cidx = 0; cidx < kCols; ++cidx) {
-                        A[cidx] = __fmaf_rn(A[cidx], a, __fmul_rn(part[u][cidx], bcoef));
+                    for (int u = 0; u < kAhead; ++u) {
+                        const bool there = j0 + u < tiles.count;
+                        ml[u] = there ? __ldg(reinterpret_cast<const float2*>(part_ml + (slot0 + j0 + u) * 2)) : make_float2(0.0f, 0.0f);
+                        #pragma unroll
+                        for (int k = 0; k < KCOLS; ++k) {
+                            const int col = lane + 32 * k;
+                            part[u][k] = (there && col < d) ? __ldg(part_o + (slot0 + j0 + u) * d + col) : 0.0f;
+                        }
+                    }
+                    #pragma unroll
+                    for (int u = 0; u < kAhead; ++u) {
+                        if (j0 + u < tiles.count) {
+                            float Mn, a, b;
+                            fold_coefficients(m1, ml[u].x, Mn, a, b);
+                            l1 = __fmaf_rn(l1, a, __fmul_rn(ml[u].y, b));
+                            m1 = Mn;
+                            #pragma unroll
+                            for (int k = 0; k < KCOLS; ++k) a1[k] = fold_value(a1[k], a, part[u][k], b);
+                        }
                     }
                 }
             }
+            #pragma unroll
+            for (int k = 0; k < KCOLS; ++k) {
+                const int col = lane + 32 * k;
+                if (col < d) seg_o[size_t(sl) * d + col] = a1[k];
+            }
+            if (lane == 0) {
+                seg_ml[sl * 2] = m1;
+                seg_ml[sl * 2 + 1] = l1;
+            }
         }
-        M = chunk_max;
+        __syncthreads();
+        // The second fold (every thread carries M and L: the same chain, the same bits).
+        for (int sl = 0; sl < count; ++sl) {
+            const float m1 = seg_ml[sl * 2];
+            if (m1 == neg_inf) continue;            // no tile of this segment is on this rank
+            float Mn, a, b;
+            fold_coefficients(M, m1, Mn, a, b);
+            L = __fmaf_rn(L, a, __fmul_rn(seg_ml[sl * 2 + 1], b));
+            M = Mn;
+            #pragma unroll
+            for (int cidx = 0; cidx < 2; ++cidx) {
+                const int col = tid + cidx * kMergeThreads;
+                if (col < d) A[cidx] = fold_value(A[cidx], a, seg_o[size_t(sl) * d + col], b);
+            }
+        }
     }
-
     #pragma unroll
-    for (int cidx = 0; cidx < kCols; ++cidx) {
-        const int i = tid + cidx * threads;
-        if (i < d) write_result(ep, size_t(b), shape.q_heads, head, d, i, A[cidx], M, L);
+    for (int cidx = 0; cidx < 2; ++cidx) {
+        const int col = tid + cidx * kMergeThreads;
+        if (col < d) write_result(ep, size_t(r), shape.q_heads, head, d, col, A[cidx], M, L);
     }
 }
 
-// ---- prefill: one (kv head, token) per CTA, tiles folded in place ------------------------------
+// ---- merge for many rows of few segments: the second fold over segment partials ----------------------
+// Rows are the query tokens of one prefill chunk (row r is the token at first_position + r and shares
+// its slots with the other tokens of its 128-row tile) or the entries of a decode batch.
+struct MergeRows {
+    int decode;              // 1: rows are batch entries at meta.pos[]
+    int first_position;      // prefill
+    int tokens;              // query tokens, or batch entries
+    int tokens_per_tile;     // prefill: 128 / group
+    BatchMeta meta;
+};
+
+// A warp per row,
+// eight rows per block, lane l holding columns (k * 32 + l) * VEC .. + VEC - 1 for k < K.  The
+// partials of four segments are fetched before the dependent chain that folds them.
+constexpr int kMergeRowsPerBlock = 8;
+
+template <int VEC, int K>
+__global__ void __launch_bounds__(kMergeRowsPerBlock * 32)
+merge_rows_kernel(const AttnShape shape, const RowMap map, const MergeRows rows, const float* __restrict__ part_o,
+                  const float* __restrict__ part_ml, int slots, const EpilogueArgs ep) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const size_t row = size_t(blockIdx.x) * kMergeRowsPerBlock + (threadIdx.x >> 5);    // token * q_heads + head
+    if (row >= size_t(rows.tokens) * shape.q_heads) return;
+    const int r = int(row / shape.q_heads);
+    const int head = int(row - size_t(r) * shape.q_heads);
+    const int d = shape.head_dim;
+    int first_pos, last_pos;
+    if (rows.decode) {
+        first_pos = last_pos = rows.meta.pos[r];
+    } else {
+        const int tile_row0 = (r / rows.tokens_per_tile) * rows.tokens_per_tile;
+        first_pos = rows.first_position + tile_row0;
+        last_pos = rows.first_position + min(tile_row0 + rows.tokens_per_tile, rows.tokens) - 1;
+    }
+    const int n_parts = min(visible_groups(first_pos, last_pos, shape.window, map.log_segment), slots);
+
+    float M, L;
+    if (shape.count_sink) {
+        const uint16_t bits = shape.sinks ? shape.sinks[head] : kNoSinkBits;
+        M = __fmul_rn(bf16_bits_to_float(bits), kLog2e);
+        L = 1.0f;
+    } else {
+        M = kEmptyMax;
+        L = 0.0f;
+    }
+    float A[K][VEC];
+    #pragma unroll
+    for (int k = 0; k < K; ++k) {
+        #pragma unroll
+        for (int v = 0; v < VEC; ++v) A[k][v] = 0.0f;
+    }
+    constexpr int kAhead = 4;
+    for (int s0 = 0; s0 < n_parts; s0 += kAhead) {
+        float part[kAhead][K][VEC];
+        float2 ml[kAhead];
+        bool present[kAhead];
+        #pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            const int s = s0 + u;
+            // A slot no thread block wrote (this rank owns no tile of that segment) is skipped.
+            present[u] = s < n_parts && (map.world <= 1 || group_tiles(map, first_pos, last_pos, shape.window, s, map.log_segment).count > 0);
+            ml[u] = make_float2(0.0f, 0.0f);
+            if (present[u]) ml[u] = __ldg(reinterpret_cast<const float2*>(part_ml + (row * slots + s) * 2));
+            const float* src = part_o + (row * slots + s) * d;
+            #pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const int col = (k * 32 + lane) * VEC;
+                if constexpr (VEC == 4) {
+                    float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (present[u] && col < d) x = __ldg(reinterpret_cast<const float4*>(src + col));
+                    part[u][k][0] = x.x; part[u][k][1] = x.y; part[u][k][2] = x.z; part[u][k][3] = x.w;
+                } else if constexpr (VEC == 2) {
+                    float2 x = make_float2(0.0f, 0.0f);
+                    if (present[u] && col < d) x = __ldg(reinterpret_cast<const float2*>(src + col));
+                    part[u][k][0] = x.x; part[u][k][1] = x.y;
+                } else {
+                    part[u][k][0] = (present[u] && col < d) ? __ldg(src + col) : 0.0f;
+                }
+            }
+        }
+        #pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            if (!present[u]) continue;
+            float Mn, a, b;
+            fold_coefficients(M, ml[u].x, Mn, a, b);
+            L = __fmaf_rn(L, a, __fmul_rn(ml[u].y, b));
+            M = Mn;
+            #pragma unroll
+            for (int k = 0; k < K; ++k) {
+                #pragma unroll
+                for (int v = 0; v < VEC; ++v) A[k][v] = fold_value(A[k][v], a, part[u][k][v], b);
+            }
+        }
+    }
+    #pragma unroll
+    for (int k = 0; k < K; ++k) {
+        #pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+            const int col = (k * 32 + lane) * VEC + v;
+            if (col < d) write_result(ep, size_t(r), shape.q_heads, head, d, col, A[k][v], M, L);
+        }
+    }
+}
+
+// ---- prefill: one (kv head, token) per CTA: the first fold per segment, the second in place -------
 __global__ void __launch_bounds__(kThreads)
 prefill_rows_kernel(const AttnShape shape, const CacheView cache, int seq,
                     const uint16_t* __restrict__ q, int first_position, const EpilogueArgs ep) {
@@ -407,53 +560,51 @@ prefill_rows_kernel(const AttnShape shape, const CacheView cache, int seq,
     const int kv_head = blockIdx.x;
     const int token = blockIdx.y;
     const int position = first_position + token;
-    int lo, first_tile, last_tile;
-    tile_span(position, shape.window, lo, first_tile, last_tile);
+    const int lo = shape.window > 0 ? max(0, position - shape.window + 1) : 0;
 
-    float *A, *M, *L;
-    SimtSmem sm = carve(raw, G, d, true, &A, &M, &L);
+    FoldState st[2];                              // st[0]: the current segment; st[1]: the row
+    SimtSmem sm = carve(raw, G, d, 2, st);
     load_group_queries(sm, q + (size_t(token) * shape.q_heads + size_t(kv_head) * G) * d, G, d);
-    for (int i = threadIdx.x; i < G * d; i += kThreads) A[i] = 0.0f;
+    for (int i = threadIdx.x; i < G * d; i += kThreads) st[1].A[i] = 0.0f;
     if (threadIdx.x < G) {
         if (shape.count_sink) {
             const int head = kv_head * G + threadIdx.x;
             const uint16_t bits = shape.sinks ? shape.sinks[head] : kNoSinkBits;
-            M[threadIdx.x] = __fmul_rn(bf16_bits_to_float(bits), kLog2e);
-            L[threadIdx.x] = 1.0f;
+            st[1].M[threadIdx.x] = __fmul_rn(bf16_bits_to_float(bits), kLog2e);
+            st[1].L[threadIdx.x] = 1.0f;
         } else {
-            M[threadIdx.x] = kEmptyMax;
-            L[threadIdx.x] = 0.0f;
+            st[1].M[threadIdx.x] = kEmptyMax;
+            st[1].L[threadIdx.x] = 0.0f;
         }
     }
     __syncthreads();
 
     const size_t head_rows = (size_t(seq) * cache.kv_heads + kv_head) * cache.capacity;
-    const int world = max(cache.map.world, 1);
-    for (int tile = first_tile; tile <= last_tile; ++tile) {
-        if (world > 1 && (tile % world) != cache.map.rank) continue;
-        const size_t row0 = head_rows + row_of_tile(cache.map, tile);
-        tile_partial(sm, cache.k + row0 * d, cache.v + row0 * d, tile * kTileKeys, lo, position, G,
-                     d, shape.c);
+    const int n_slots = visible_groups(position, position, shape.window, cache.map.log_segment);
+    for (int slot = 0; slot < n_slots; ++slot) {
+        const TileRange tiles = group_tiles(cache.map, position, position, shape.window, slot, cache.map.log_segment);
+        if (tiles.count <= 0) continue;
+        segment_partial(sm, st[0], cache, head_rows, tiles, lo, position, G, d, shape.c);
         for (int i = threadIdx.x; i < G * d; i += kThreads) {
             const int g = i / d;
             float Mn, a, b;
-            fold_coefficients(M[g], sm.mm[g], Mn, a, b);
-            A[i] = fold_value(A[i], a, sm.acc[i], b);
+            fold_coefficients(st[1].M[g], st[0].M[g], Mn, a, b);
+            st[1].A[i] = fold_value(st[1].A[i], a, st[0].A[i], b);
         }
         __syncthreads();
         if (threadIdx.x < G) {
             const int g = threadIdx.x;
             float Mn, a, b;
-            fold_coefficients(M[g], sm.mm[g], Mn, a, b);
-            L[g] = __fmaf_rn(L[g], a, __fmul_rn(sm.l[g], b));
-            M[g] = Mn;
+            fold_coefficients(st[1].M[g], st[0].M[g], Mn, a, b);
+            st[1].L[g] = __fmaf_rn(st[1].L[g], a, __fmul_rn(st[0].L[g], b));
+            st[1].M[g] = Mn;
         }
         __syncthreads();
     }
 
     for (int i = threadIdx.x; i < G * d; i += kThreads) {
         const int g = i / d;
-        write_result(ep, size_t(token), shape.q_heads, kv_head * G + g, d, i - g * d, A[i], M[g], L[g]);
+        write_result(ep, size_t(token), shape.q_heads, kv_head * G + g, d, i - g * d, st[1].A[i], st[1].M[g], st[1].L[g]);
     }
 }
 
@@ -487,7 +638,7 @@ hc_status simt_prefill(hc_context* ctx, const AttnShape& shape, const CacheView&
                        const uint16_t* q, int tokens, int first_position, const EpilogueArgs& ep,
                        cudaStream_t stream) {
     if (tokens <= 0) return HC_OK;
-    const size_t smem = simt_smem_bytes(shape.group, shape.head_dim, true);
+    const size_t smem = simt_smem_bytes(shape.group, shape.head_dim, 2);
     cudaError_t err = cudaFuncSetAttribute(prefill_rows_kernel,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (err != cudaSuccess) return check_cuda(err, "prefill_rows_kernel shared memory");
@@ -517,50 +668,122 @@ hc_status simt_prefill(hc_context* ctx, const AttnShape& shape, const CacheView&
     return HC_OK;
 }
 
+DecodePlan plan_decode(const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq, int target_items,
+                       bool allow_whole, int max_log_run) {
+    DecodePlan plan{};
+    int most_tiles = 0;
+    for (int b = 0; b < n_seq; ++b) most_tiles = std::max(most_tiles, row_tiles(map, meta.pos[b], meta.pos[b], shape.window).count);
+    plan.tiles = std::max(most_tiles, 1);
+    // The coarsest cut that still gives the machine enough items: whole rows, then segments, then
+    // shorter and shorter runs of tiles.  Rows of a tile or two are never cut: the merge would cost
+    // more than it saves.
+    if (allow_whole && (most_tiles <= 2 || n_seq * shape.kv_heads >= target_items)) {
+        plan.finish = 1;
+        plan.log_run = map.log_segment;
+        plan.slots = 1;
+        return plan;
+    }
+    int log_run = std::max(max_log_run, map.log_segment);
+    for (; log_run > 0; --log_run) {
+        int items = 0;
+        for (int b = 0; b < n_seq; ++b) items += visible_groups(meta.pos[b], meta.pos[b], shape.window, log_run);
+        if (items * shape.kv_heads >= target_items) break;
+    }
+    plan.log_run = log_run;
+    plan.tile_partials = log_run < map.log_segment ? 1 : 0;
+    if (plan.tile_partials) {
+        plan.slots = plan.tiles;
+    } else {
+        for (int b = 0; b < n_seq; ++b) {
+            plan.slots = std::max(plan.slots, visible_groups(meta.pos[b], meta.pos[b], shape.window, map.log_segment));
+        }
+    }
+    return plan;
+}
+
+
+DecodePlan simt_plan_decode(const hc_context* ctx, const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq) {
+    // These kernels always leave partials and merge: a whole-row plan is run as whole segments.
+    DecodePlan plan = plan_decode(shape, map, meta, n_seq, 4 * ctx->sm_count, true, map.log_segment);
+    if (plan.finish) {
+        plan.finish = 0;
+        plan.tile_partials = 0;
+        plan.log_run = map.log_segment;
+        plan.slots = 1;
+        for (int b = 0; b < n_seq; ++b) {
+            plan.slots = std::max(plan.slots, visible_groups(meta.pos[b], meta.pos[b], shape.window, map.log_segment));
+        }
+    }
+    return plan;
+}
+
 hc_status simt_decode(hc_context* ctx, const AttnShape& shape, const CacheView& cache,
                       const BatchMeta& meta, int n_seq, const uint16_t* q, const Workspace& ws,
                       const EpilogueArgs& ep, cudaStream_t stream) {
     if (n_seq <= 0) return HC_OK;
-    const int world = cache.map.world > 1 ? cache.map.world : 1;
-    int max_tiles = 0;
-    for (int b = 0; b < n_seq; ++b) {
-        int lo, first_tile, last_tile;
-        tile_span(meta.pos[b], shape.window, lo, first_tile, last_tile);
-        int n = last_tile - first_tile + 1;
-        if (world > 1) n = (n + world - 1) / world + 1;
-        if (n > max_tiles) max_tiles = n;
-    }
+    const DecodePlan plan = simt_plan_decode(ctx, shape, cache.map, meta, n_seq);
     const size_t rows = size_t(n_seq) * shape.q_heads;
-    if (rows * max_tiles * shape.head_dim > ws.part_o_floats || rows * max_tiles * 2 > ws.part_ml_floats) {
+    if (rows * plan.slots * shape.head_dim > ws.part_o_floats || rows * plan.slots * 2 > ws.part_ml_floats) {
         return fail(HC_KV_OVERFLOW, "decode: the split-attention workspace is too small for this call");
     }
-    const size_t smem = simt_smem_bytes(shape.group, shape.head_dim, false);
-    cudaError_t err = cudaFuncSetAttribute(decode_tiles_kernel,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (err != cudaSuccess) return check_cuda(err, "decode_tiles_kernel shared memory");
-    dim3 grid(max_tiles, shape.kv_heads, n_seq);
-    decode_tiles_kernel<<<grid, kThreads, smem, stream>>>(shape, cache, meta, q, ws.part_o,
-                                                         ws.part_ml, max_tiles);
+    int runs = 1;
+    for (int b = 0; b < n_seq; ++b) runs = std::max(runs, visible_groups(meta.pos[b], meta.pos[b], shape.window, plan.log_run));
+    const size_t smem = simt_smem_bytes(shape.group, shape.head_dim, 1);
+    cudaError_t err = cudaFuncSetAttribute(decode_runs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (err != cudaSuccess) return check_cuda(err, "decode_runs_kernel shared memory");
+    dim3 grid(runs, shape.kv_heads, n_seq);
+    decode_runs_kernel<<<grid, kThreads, smem, stream>>>(shape, cache, meta, q, ws.part_o, ws.part_ml, plan.slots,
+                                                         plan.log_run, plan.tile_partials);
     ctx->launches += 1;
     err = cudaGetLastError();
-    if (err != cudaSuccess) return check_cuda(err, "decode_tiles_kernel launch");
-    return launch_merge(ctx, shape, meta, n_seq, ws, max_tiles, world, cache.map.rank, ep, stream);
+    if (err != cudaSuccess) return check_cuda(err, "decode_runs_kernel launch");
+    return launch_merge_decode(ctx, shape, cache.map, meta, n_seq, ws, plan, ep, stream);
 }
 
-hc_status launch_merge(hc_context* ctx, const AttnShape& shape, const BatchMeta& meta, int n_seq,
-                       const Workspace& ws, int part_tiles, int world, int rank, const EpilogueArgs& ep,
-                       cudaStream_t stream) {
-    dim3 mgrid(shape.q_heads, n_seq);
+static hc_status launch_merge_rows(hc_context* ctx, const AttnShape& shape, const RowMap& map, const MergeRows& rows,
+                                   const Workspace& ws, int slots, const EpilogueArgs& ep, cudaStream_t stream) {
     const int d = shape.head_dim;
-    const int threads = d <= 64 ? 64 : kThreads;
-    const int cols = (d + threads - 1) / threads;
-    auto kernel = cols <= 1 ? merge_tiles_kernel<1> : cols == 2 ? merge_tiles_kernel<2> : merge_tiles_kernel<4>;
-    const cudaError_t launched = launch_pdl(kernel, mgrid, dim3(threads), 0, stream, shape, meta,
+    auto kernel = d == 64 ? merge_rows_kernel<2, 1> : d == 128 ? merge_rows_kernel<4, 1> : d == 256 ? merge_rows_kernel<4, 2>
+                : d == 512 ? merge_rows_kernel<4, 4> : merge_rows_kernel<1, 16>;
+    const size_t n_rows = size_t(rows.tokens) * shape.q_heads;
+    const unsigned blocks = unsigned((n_rows + kMergeRowsPerBlock - 1) / kMergeRowsPerBlock);
+    const cudaError_t launched = launch_pdl(kernel, dim3(blocks), dim3(kMergeRowsPerBlock * 32), 0, stream, shape, map, rows,
                                             static_cast<const float*>(ws.part_o), static_cast<const float*>(ws.part_ml),
-                                            part_tiles, world, rank, ep);
+                                            slots, ep);
     ctx->launches += 1;
-    if (launched != cudaSuccess) return check_cuda(launched, "merge_tiles_kernel launch");
-    return check_cuda(cudaGetLastError(), "merge_tiles_kernel launch");
+    if (launched != cudaSuccess) return check_cuda(launched, "merge_rows_kernel launch");
+    return check_cuda(cudaGetLastError(), "merge_rows_kernel launch");
+}
+
+hc_status launch_merge_decode(hc_context* ctx, const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq,
+                              const Workspace& ws, const DecodePlan& plan, const EpilogueArgs& ep, cudaStream_t stream) {
+    if (!plan.tile_partials && plan.slots <= 8) {
+        // Few segment partials a row: a warp per row does it without the staging below.
+        MergeRows rows{};
+        rows.decode = 1;
+        rows.tokens = n_seq;
+        rows.meta = meta;
+        return launch_merge_rows(ctx, shape, map, rows, ws, plan.slots, ep, stream);
+    }
+    const int d = shape.head_dim;
+    const int kcols = (d + 31) / 32;
+    auto kernel = kcols <= 2 ? merge_decode_kernel<2> : kcols <= 4 ? merge_decode_kernel<4>
+                : kcols <= 8 ? merge_decode_kernel<8> : merge_decode_kernel<16>;
+    const cudaError_t launched = launch_pdl(kernel, dim3(shape.q_heads, n_seq), dim3(kMergeThreads), merge_smem_bytes(d), stream,
+                                            shape, map, meta, static_cast<const float*>(ws.part_o),
+                                            static_cast<const float*>(ws.part_ml), plan.slots, plan.tile_partials, ep);
+    ctx->launches += 1;
+    if (launched != cudaSuccess) return check_cuda(launched, "merge_decode_kernel launch");
+    return check_cuda(cudaGetLastError(), "merge_decode_kernel launch");
+}
+
+hc_status launch_merge_prefill(hc_context* ctx, const AttnShape& shape, const RowMap& map, int tokens, int first_position,
+                               const Workspace& ws, int slots, const EpilogueArgs& ep, cudaStream_t stream) {
+    MergeRows rows{};
+    rows.first_position = first_position;
+    rows.tokens = tokens;
+    rows.tokens_per_tile = kTileKeys / shape.group;        // a row tile is 128 rows: 128 / group tokens
+    return launch_merge_rows(ctx, shape, map, rows, ws, slots, ep, stream);
 }
 
 hc_status launch_combine(hc_context* ctx, const float* gathered, int world, int rows, int q_heads,
@@ -627,16 +850,14 @@ hc_status hc_attention_decode_static(hc_context* ctx, hc_kv_cache* cache, int la
                                         &view, &meta, &ep, &store, &tensor);
     if (st != HC_OK) return st;
     if (!ctx->static_scratch) return fail(HC_CUDA_ERROR, "this context has no static scratch address");
-    int max_tiles = 0;
-    for (int b = 0; b < n_seq; ++b) {
-        int lo, first_tile, last_tile;
-        tile_span(meta.pos[b], shape.window, lo, first_tile, last_tile);
-        max_tiles = std::max(max_tiles, last_tile - first_tile + 1);
-    }
-    // Partials: [rows][tiles][d] then [rows][tiles][2].
+    // The cut the default path would make (given this much room), and its partials: [rows][slots][2]
+    // first, then [rows][slots][d].  A whole-row cut leaves no partials; the tensor-core kernels then
+    // keep their second-fold state, if any, where the partials would be.
+    const DecodePlan plan = tensor ? tc_plan_decode(ctx, shape, view.map, meta, n_seq, kStaticScratchFloats)
+                                   : simt_plan_decode(ctx, shape, view.map, meta, n_seq);
     const size_t rows = size_t(n_seq) * shape.q_heads;
-    const size_t o_floats = rows * max_tiles * shape.head_dim;
-    const size_t need = o_floats + rows * max_tiles * 2;
+    const size_t ml_floats = plan.finish ? 0 : (rows * plan.slots * 2 + 3) & ~size_t(3);
+    const size_t need = plan.finish ? 0 : ml_floats + rows * plan.slots * shape.head_dim;
     if (need > kStaticScratchFloats) {
         return fail(HC_KV_OVERFLOW, "hc_attention_decode_static: this call needs " + std::to_string(need * 4) +
                                         " bytes of partials, the fixed scratch holds " +
@@ -645,10 +866,10 @@ hc_status hc_attention_decode_static(hc_context* ctx, hc_kv_cache* cache, int la
     // Every partial the merge reads is written by this call's split kernel first, so nothing in the
     // array has to start at zero.
     Workspace ws;
-    ws.part_o = ctx->static_scratch;
-    ws.part_ml = ctx->static_scratch + o_floats;
-    ws.part_o_floats = o_floats;
-    ws.part_ml_floats = rows * max_tiles * 2;
+    ws.part_ml = ctx->static_scratch;
+    ws.part_ml_floats = ml_floats;
+    ws.part_o = ctx->static_scratch + ml_floats;
+    ws.part_o_floats = kStaticScratchFloats - ml_floats;
     // The same kernels, in the same order, as hc_attention_decode: only the partials live elsewhere,
     // so the two entry points return the same bits.
     if (tensor) {

@@ -71,7 +71,8 @@ struct TcLayout {
     static constexpr int kOnesBytes = kTileKeys * 128;       // a 128-row block of bf16 1.0 (16 KiB)
     // Staging for the epilogue's coalesced stores: 4 warps x 32 rows x 128 bytes.  With d = 128 the
     // block of ones is not used by any MMA and serves.
-    static constexpr int kEpiBytes = kSumOnTensor ? 4 * 32 * 128 : 0;
+    static constexpr int kEpiWarpBytes = 32 * 128;
+    static constexpr int kEpiBytes = kSumOnTensor ? 4 * kEpiWarpBytes : 0;
     static constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kQBytes + 2 * kStages * kTileBytes + kOnesBytes + kEpiBytes;
 };
 
@@ -84,13 +85,20 @@ struct TcBarriers {
     int abort_flag;
     float mm[8][kRows];       // per-tile scaled maxima, softmax -> fold (ring of 8 tiles)
     float l[8][kRows];        // per-tile row sums (when not summed on the tensor core)
+    float m2[kRows], l2[kRows];   // the rows' second fold between segments
 };
 
 
-template <int D>
+// MODE says what becomes of an item's rows (TcArgs: finish, tile_partials), so that a launch carries
+// the code of its own way only: 0 = the kernel finishes them, 1 = segment partials, 2 = tile partials.
+constexpr int kModeFinish = 0, kModeSegments = 1, kModeTiles = 2;
+
+template <int D, int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                     const TcArgs args) {
+    constexpr bool kFinish = MODE == kModeFinish;
+    constexpr bool kTilePartials = MODE == kModeTiles;
     using LT = TcLayout<D>;
     extern __shared__ unsigned char raw_smem[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
@@ -570,6 +578,24 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         const int t_local = row >> args.log_group;
         const int g = row & (G - 1);
         const uint32_t lane_base = uint32_t(quad * 32) << 16;
+        // Where this thread's row keeps the values of its second fold between segments.
+        constexpr int kStateStride = kRows;
+        auto state_of_row = [&]() -> float* {
+            return args.row_state + size_t(blockIdx.x) * (D * kRows) + row;
+        };
+        // (M, L) the second fold stands at: what the last segment end left, or the seed.
+        auto second_fold_state = [&](bool state_holds, uint16_t sink, float& M2, float& L2) {
+            if (state_holds) {
+                M2 = bars->m2[row];
+                L2 = bars->l2[row];
+            } else if (args.count_sink) {
+                M2 = __fmul_rn(bf16_bits_to_float(sink), kLog2e);
+                L2 = 1.0f;
+            } else {
+                M2 = kEmptyMax;
+                L2 = 0.0f;
+            }
+        };
         // The tile's row sum: from the tensor core (column D of the O buffer) or the two halves' sums.
         // Issued before the loads of O so that one wait covers both.
         auto tile_sum = [&](uint32_t o_tmem, uint32_t t) -> uint32_t {
@@ -579,9 +605,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         uint32_t t = 0, it = 0;
         bool ok = true;
         TcItemIter walk = items_begin(args);
-        // The head's sink is fetched one item ahead (prefill only: decode writes raw partials and the
-        // merge kernel seeds the fold), so its latency never sits at an item's start.
-        const bool wants_sink = args.count_sink && args.sinks != nullptr && !args.decode;
+        // The head's sink is fetched one item ahead (only when this kernel runs the second fold), so its
+        // latency never sits at an item's start.
+        const bool wants_sink = kFinish && args.count_sink && args.sinks != nullptr;
         uint16_t sink_bits = kNoSinkBits;
         if (wants_sink && walk.item < args.n_items) sink_bits = args.sinks[walk.w.kv_head * G + g];
         while (ok && walk.item < args.n_items) {
@@ -590,31 +616,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const int head = w.kv_head * G + g;
             const bool valid = t_local < w.valid_tokens;
             const bool warp_has_rows = quad * 32 < (w.valid_tokens << args.log_group);   // warp-uniform
-            float M, L;
-            if (args.count_sink) {
-                M = __fmul_rn(bf16_bits_to_float(sink_bits), kLog2e);
-                L = 1.0f;
-            } else {
-                M = kEmptyMax;
-                L = 0.0f;
-            }
+            const uint16_t item_sink = sink_bits;
             if (wants_sink && walk.item < args.n_items) sink_bits = args.sinks[walk.w.kv_head * G + g];
-            float A[D];
-            #pragma unroll
-            for (int i = 0; i < D; ++i) A[i] = 0.0f;
-            for (int j = 0; j < w.n_tiles; ++j, ++t) {
-                if (!mbar_wait(&bars->o_full, t & 1, abort_flag, args.status, 9)) { ok = false; break; }
-                tc_fence_after();
-                if (!warp_has_rows) {
-                    tc_fence_before();
-                    mbar_arrive(&bars->o_free);
-                    continue;
-                }
-                const uint32_t o_tmem = tmem + lane_base + LT::kOCol0;
-                const uint32_t l_bits = tile_sum(o_tmem, t);   // valid after the first wait below
-                if (args.decode) {
-                    // Split decode: the tile's partial goes to the workspace; merge_tiles_kernel folds.
-                    const size_t prow = (size_t(w.row0) * args.q_heads + head) * args.part_tiles + (w.ordinal0 + j);
+            if constexpr (kTilePartials) {
+                // Finely split decode: every tile's own partial goes to the workspace, both folds to the merge.
+                for (int j = 0; j < w.n_tiles; ++j, ++t) {
+                    if (!mbar_wait(&bars->o_full, t & 1, abort_flag, args.status, 9)) { ok = false; break; }
+                    tc_fence_after();
+                    if (!warp_has_rows) {
+                        tc_fence_before();
+                        mbar_arrive(&bars->o_free);
+                        continue;
+                    }
+                    const uint32_t o_tmem = tmem + lane_base + LT::kOCol0;
+                    const uint32_t l_bits = tile_sum(o_tmem, t);   // valid after the first wait below
+                    const size_t prow = (size_t(w.row0) * args.q_heads + head) * args.slots + (w.slot + j);
                     #pragma unroll
                     for (int hb = 0; hb < D / 64; ++hb) {
                         uint32_t o[2][32];
@@ -638,44 +654,151 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         }
                     }
                     if (valid) {
-                        args.part_ml[prow * 2] = bars->mm[t & 7][row];
-                        args.part_ml[prow * 2 + 1] = __uint_as_float(l_bits);
+                        *reinterpret_cast<float2*>(args.part_ml + prow * 2) =
+                            make_float2(bars->mm[t & 7][row], __uint_as_float(l_bits));
                     }
-                    continue;
                 }
-                float Mn, a, b;
-                #pragma unroll
-                for (int hb = 0; hb < D / 64; ++hb) {
-                    uint32_t o[2][32];
-                    HC_TMEM_LD32(o_tmem + hb * 64, o[0]);
-                    HC_TMEM_LD32(o_tmem + hb * 64 + 32, o[1]);
-                    if (hb == 0) fold_coefficients(M, bars->mm[t & 7][row], Mn, a, b);   // while the loads fly
-                    tc_wait_ld();
-                    if (hb == D / 64 - 1) {
+                ++it;
+                continue;
+            }
+            // The running segment's partial: a fold over its tiles from the empty state.
+            float M = kEmptyMax, L = 0.0f;
+            float A[D];
+            #pragma unroll
+            for (int i = 0; i < D; ++i) A[i] = 0.0f;
+            // One pass per segment the item touches.  With finish, the row's second fold runs between
+            // the passes.  Its state is kept out of the registers: (M2, L2) in shared memory, the values
+            // in global memory (element i of this thread's row at state[i * kStateStride]; it stays in L2);
+            // both are untouched
+            // until the item's first segment is complete, which a tile's segment index tells.
+            for (int j = 0; ok && j < w.n_tiles;) {
+                const int pass_tile = w.tile_first + j * world;
+                const int pass_last = (((pass_tile >> args.map.log_segment) + 1) << args.map.log_segment) - 1;
+                const int pass_end = min(w.n_tiles, j + (pass_last - pass_tile) / world + 1);
+                // The first fold over the segment's tiles.
+                for (; j < pass_end; ++j, ++t) {
+                    if (!mbar_wait(&bars->o_full, t & 1, abort_flag, args.status, 9)) { ok = false; break; }
+                    tc_fence_after();
+                    if (!warp_has_rows) {
                         tc_fence_before();
                         mbar_arrive(&bars->o_free);
+                        continue;
                     }
-                    if (hb == 0) {
-                        L = __fmaf_rn(L, a, __fmul_rn(__uint_as_float(l_bits), b));
-                        M = Mn;
-                    }
+                    const uint32_t o_tmem = tmem + lane_base + LT::kOCol0;
+                    const uint32_t l_bits = tile_sum(o_tmem, t);   // valid after the first wait below
+                    float Mn, a, b;
                     #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
+                    for (int hb = 0; hb < D / 64; ++hb) {
+                        uint32_t o[2][32];
+                        HC_TMEM_LD32(o_tmem + hb * 64, o[0]);
+                        HC_TMEM_LD32(o_tmem + hb * 64 + 32, o[1]);
+                        if (hb == 0) fold_coefficients(M, bars->mm[t & 7][row], Mn, a, b);   // while the loads fly
+                        tc_wait_ld();
+                        if (hb == D / 64 - 1) {
+                            tc_fence_before();
+                            mbar_arrive(&bars->o_free);
+                        }
+                        if (hb == 0) {
+                            L = __fmaf_rn(L, a, __fmul_rn(__uint_as_float(l_bits), b));
+                            M = Mn;
+                        }
                         #pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const int col = hb * 64 + u * 32 + i;
-                            fold_value2(A[col], A[col + 1], a, o[u][i], o[u][i + 1], b);
+                        for (int u = 0; u < 2; ++u) {
+                            #pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                const int col = hb * 64 + u * 32 + i;
+                                fold_value2(A[col], A[col + 1], a, o[u][i], o[u][i + 1], b);
+                            }
                         }
                     }
                 }
+                if constexpr (!kFinish) {
+                    // The segment's partial goes to the workspace (a merge kernel runs the second fold), and
+                    // the next segment of the run starts over.
+                    if (ok && valid) {
+                        const int slot = (pass_tile >> args.map.log_segment) - w.first_segment;
+                        const size_t prow = ((size_t(w.row0 + t_local)) * args.q_heads + head) * args.slots + slot;
+                        float* dst = args.part_o + prow * D;
+                        #pragma unroll
+                        for (int i = 0; i < D; i += 4) {
+                            *reinterpret_cast<float4*>(dst + i) = make_float4(A[i], A[i + 1], A[i + 2], A[i + 3]);
+                        }
+                        *reinterpret_cast<float2*>(args.part_ml + prow * 2) = make_float2(M, L);
+                    }
+                    if (j < w.n_tiles) {
+                        #pragma unroll
+                        for (int i = 0; i < D; ++i) A[i] = 0.0f;
+                        M = kEmptyMax;
+                        L = 0.0f;
+                    }
+                }
+                if (kFinish && ok && warp_has_rows && j < w.n_tiles) {
+                    // A segment is complete and another follows: fold it into the row's state and start over.
+                    const int tile = w.tile_first + (j - 1) * world;
+                    const bool state_holds = (tile >> args.map.log_segment) != (w.tile_first >> args.map.log_segment);
+                    float M2, L2;
+                    second_fold_state(state_holds, item_sink, M2, L2);
+                    float Mn2, a2, b2;
+                    fold_coefficients(M2, M, Mn2, a2, b2);
+                    bars->m2[row] = Mn2;
+                    bars->l2[row] = __fmaf_rn(L2, a2, __fmul_rn(L, b2));
+                    float* const state = state_of_row();
+                    #pragma unroll
+                    for (int i0 = 0; i0 < D; i0 += 16) {
+                        float before[16];
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) before[i] = state_holds ? state[(i0 + i) * kStateStride] : 0.0f;
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            state[(i0 + i) * kStateStride] = fold_value(before[i], a2, A[i0 + i], b2);
+                            A[i0 + i] = 0.0f;
+                        }
+                        asm volatile("" ::: "memory");      // sixteen values in flight, not all of them
+                    }
+                    M = kEmptyMax;
+                    L = 0.0f;
+                }
             }
             if (!ok) break;
-            if (!args.decode && warp_has_rows && !args.ep.write_partial && args.ep.gate_layout == HC_GATE_NONE &&
+            const size_t out_row = size_t(w.row0 + t_local);
+            if constexpr (!kFinish) {
+                ++it;
+                continue;
+            }
+            // The row's last segment: the last step of the second fold, which started from the sink (or,
+            // on the ranks of a sequence-sharded cache that do not count it, from the empty state).
+            {
+                const int last_tile = w.tile_first + (w.n_tiles - 1) * world;
+                const bool state_holds = warp_has_rows && (last_tile >> args.map.log_segment) != (w.tile_first >> args.map.log_segment);
+                float M2, L2;
+                second_fold_state(state_holds, item_sink, M2, L2);
+                float Mn, a, b;
+                fold_coefficients(M2, M, Mn, a, b);
+                L = __fmaf_rn(L2, a, __fmul_rn(L, b));
+                M = Mn;
+                const float* const state = state_of_row();
+                if (state_holds) {
+                    #pragma unroll
+                    for (int i0 = 0; i0 < D; i0 += 16) {
+                        float before[16];
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) before[i] = state[(i0 + i) * kStateStride];
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) A[i0 + i] = fold_value(before[i], a, A[i0 + i], b);
+                        asm volatile("" ::: "memory");
+                    }
+                } else {
+                    // fold_value(0, a, A, b) = 0 * a + A * b = A * b exactly: one multiply.
+                    #pragma unroll
+                    for (int i = 0; i < D; ++i) A[i] = __fmul_rn(A[i], b);
+                }
+            }
+            if (warp_has_rows && !args.ep.write_partial && args.ep.gate_layout == HC_GATE_NONE &&
                 args.ep.io_dtype != HC_F32) {
                 // bf16 output without a gate (warp-uniform): rows go through shared memory so that a
                 // store instruction writes whole 128-byte lines (the G heads of a token are adjacent
                 // in memory) instead of 16 bytes of 32 different rows.
-                unsigned char* stage = epi_smem + (warp & 3) * (32 * 128);
+                unsigned char* stage = epi_smem + (warp & 3) * LT::kEpiWarpBytes;
                 uint16_t* out16 = reinterpret_cast<uint16_t*>(args.ep.out);
                 #pragma unroll
                 for (int b = 0; b < D / 64; ++b) {
@@ -705,8 +828,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     }
                     __syncwarp();
                 }
-            } else if (valid && !args.decode) {
-                const size_t out_row = size_t(w.row0 + t_local);
+            } else if (valid) {
                 if (args.ep.write_partial) {
                     float* dst = reinterpret_cast<float*>(args.ep.out) + (out_row * args.q_heads + head) * size_t(D + 2);
                     // A partial row is D + 2 floats: its start is 8-byte aligned, not 16.
@@ -814,19 +936,19 @@ void tc_free_tensor_maps(hc_layer_store& layer) {
     layer.tmap_k = layer.tmap_v = nullptr;
 }
 
-template <int D>
-static hc_status launch_tc(hc_context* ctx, const TcArgs& args, const hc_layer_store& layer, cudaStream_t stream) {
+template <int D, int MODE>
+static hc_status launch_tc_mode(hc_context* ctx, const TcArgs& args, const hc_layer_store& layer, cudaStream_t stream) {
     using LT = TcLayout<D>;
     const int smem = LT::kSmemBytes + int(sizeof(TcBarriers));
     static bool configured[64] = {};                 // per device: the attribute is set once
     if (!configured[ctx->device & 63]) {
-        cudaError_t err = cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t err = cudaFuncSetAttribute(attention_tc_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (err != cudaSuccess) return check_cuda(err, "attention_tc_kernel shared memory");
         configured[ctx->device & 63] = true;
     }
     // Persistent: one CTA per SM at most, each walking items blockIdx.x, blockIdx.x + gridDim.x, ...
     const int grid = std::max(1, std::min(args.n_items, std::max(ctx->sm_count, 1)));
-    const cudaError_t launched = launch_pdl(attention_tc_kernel<D>, grid, kTcThreads, size_t(smem), stream,
+    const cudaError_t launched = launch_pdl(attention_tc_kernel<D, MODE>, grid, kTcThreads, size_t(smem), stream,
                                             *static_cast<const CUtensorMap*>(layer.tmap_k),
                                             *static_cast<const CUtensorMap*>(layer.tmap_v), args);
     ctx->launches += 1;
@@ -834,15 +956,17 @@ static hc_status launch_tc(hc_context* ctx, const TcArgs& args, const hc_layer_s
     return check_cuda(cudaGetLastError(), "attention_tc_kernel launch");
 }
 
-hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer, const CacheView& cache,
-                     int seq, const uint16_t* q, int tokens, int first_position, const EpilogueArgs& ep,
-                     cudaStream_t stream) {
-    if (!layer.tmap_k || !layer.tmap_v) return fail(HC_UNSUPPORTED, "this layer has no tensor maps");
-    if (tokens <= 0) return HC_OK;
-    TcArgs args{};
+template <int D>
+static hc_status launch_tc(hc_context* ctx, const TcArgs& args, const hc_layer_store& layer, cudaStream_t stream) {
+    if (args.finish) return launch_tc_mode<D, kModeFinish>(ctx, args, layer, stream);
+    if (args.tile_partials) return launch_tc_mode<D, kModeTiles>(ctx, args, layer, stream);
+    return launch_tc_mode<D, kModeSegments>(ctx, args, layer, stream);
+}
+
+// What the two launchers share.
+static void fill_common_args(TcArgs& args, hc_context* ctx, const AttnShape& shape, const CacheView& cache,
+                             const uint16_t* q, const Workspace& ws, const EpilogueArgs& ep) {
     args.q = q;
-    args.tokens = tokens;
-    args.first_position = first_position;
     args.q_heads = shape.q_heads;
     args.kv_heads = shape.kv_heads;
     int log_group = 0;
@@ -852,19 +976,83 @@ hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_sto
     args.c = shape.c;
     args.sinks = shape.sinks;
     args.count_sink = shape.count_sink;
-    args.seq = seq;
     args.map = cache.map;
     args.ep = ep;
     args.status = ctx->status_dev;
-    const int tokens_per_tile = kRows / shape.group;
-    args.mtiles = (tokens + tokens_per_tile - 1) / tokens_per_tile;
-    args.n_items = args.mtiles * shape.kv_heads;
-    args.magic_kv_heads = division_magic(uint32_t(shape.kv_heads), uint32_t(args.n_items));
-    args.magic_chunks = 0;
-    args.magic_world = division_magic(uint32_t(std::max(cache.map.world, 1)), 1u << 24);
+    args.part_o = ws.part_o;
+    args.part_ml = ws.part_ml;
+    args.row_state = ws.part_o;       // a launch uses one or the other
+}
+
+// Floats of row state a whole-row launch needs.
+static size_t row_state_floats(const hc_context* ctx, const AttnShape& shape) {
+    return size_t(std::max(ctx->sm_count, 1)) * shape.head_dim * kRows;
+}
+
+static hc_status launch_any(hc_context* ctx, const AttnShape& shape, const TcArgs& args, const hc_layer_store& layer,
+                            cudaStream_t stream) {
     if (shape.head_dim == 64) return launch_tc<64>(ctx, args, layer, stream);
     if (shape.head_dim == 128) return launch_tc<128>(ctx, args, layer, stream);
     return launch_tc256(ctx, layer.tmap_k, layer.tmap_v, &args, args.n_items, stream);
+}
+
+hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer, const CacheView& cache,
+                     int seq, const uint16_t* q, int tokens, int first_position, const Workspace& ws,
+                     const EpilogueArgs& ep, cudaStream_t stream) {
+    if (!layer.tmap_k || !layer.tmap_v) return fail(HC_UNSUPPORTED, "this layer has no tensor maps");
+    if (tokens <= 0) return HC_OK;
+    TcArgs args{};
+    fill_common_args(args, ctx, shape, cache, q, ws, ep);
+    args.tokens = tokens;
+    args.first_position = first_position;
+    args.seq = seq;
+    args.log_run = cache.map.log_segment;
+    const int tokens_per_tile = kRows / shape.group;
+    args.mtiles = (tokens + tokens_per_tile - 1) / tokens_per_tile;
+    // Segments a row tile spans, at most.
+    int slots = 1;
+    for (int mtile = 0; mtile < args.mtiles; ++mtile) {
+        const int first = first_position + mtile * tokens_per_tile;
+        const int last = first_position + std::min((mtile + 1) * tokens_per_tile, tokens) - 1;
+        slots = std::max(slots, visible_groups(first, last, shape.window, cache.map.log_segment));
+    }
+    // Whole rows per item when that alone fills the machine or nothing could be split; otherwise one
+    // item per (row tile, kv head, segment), merged afterwards.
+    const int whole_items = args.mtiles * shape.kv_heads;
+    const size_t rows = size_t(tokens) * shape.q_heads;
+    const bool can_split = slots > 1 && rows * slots * shape.head_dim <= ws.part_o_floats && rows * slots * 2 <= ws.part_ml_floats;
+    const bool can_finish = slots == 1 || row_state_floats(ctx, shape) <= ws.part_o_floats;
+    const bool whole = !can_split || (can_finish && 2 * whole_items > ctx->sm_count);
+    if (whole && !can_finish) {
+        return fail(HC_KV_OVERFLOW, "prefill: the attention workspace is too small for this chunk (" + std::to_string(tokens) +
+                                        " tokens over " + std::to_string(slots) + " segments)");
+    }
+    args.finish = whole ? 1 : 0;
+    if (whole) slots = 1;
+    args.slots = slots;
+    args.n_items = whole_items * slots;
+    args.magic_slots = division_magic(uint32_t(slots), uint32_t(args.n_items));
+    args.magic_kv_heads = division_magic(uint32_t(shape.kv_heads), uint32_t(args.n_items));
+    const hc_status st = launch_any(ctx, shape, args, layer, stream);
+    if (st != HC_OK || args.finish) return st;
+    return launch_merge_prefill(ctx, shape, cache.map, tokens, first_position, ws, slots, ep, stream);
+}
+
+DecodePlan tc_plan_decode(const hc_context* ctx, const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq,
+                          size_t part_o_floats) {
+    // About six items per thread block, so that the static round-robin balances (measured best of
+    // 3 .. 12 on uniform and ragged batches); the head_dim 256 kernel does not look ahead across
+    // items: about one per thread block.
+    const int target = (shape.head_dim == 256 ? 1 : 6) * std::max(ctx->sm_count, 1);
+    // Runs may cover several segments (one partial each): up to 64 tiles.
+    DecodePlan plan = plan_decode(shape, map, meta, n_seq, target, true, 6);
+    if (plan.finish && row_state_floats(ctx, shape) > part_o_floats) {
+        // A whole row that spans two segments needs the second fold's state, for which there is no room.
+        bool spans = false;
+        for (int b = 0; b < n_seq; ++b) spans = spans || visible_groups(meta.pos[b], meta.pos[b], shape.window, map.log_segment) > 1;
+        if (spans) plan = plan_decode(shape, map, meta, n_seq, target, false, 6);
+    }
+    return plan;
 }
 
 hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer, const CacheView& cache,
@@ -872,78 +1060,36 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
                     const EpilogueArgs& ep, cudaStream_t stream) {
     if (!layer.tmap_k || !layer.tmap_v) return fail(HC_UNSUPPORTED, "this layer has no tensor maps");
     if (n_seq <= 0) return HC_OK;
-    const int world = cache.map.world > 1 ? cache.map.world : 1;
-    int max_tiles = 0;
-    long long total_tiles = 0;
-    int seq_tile_count[kMaxBatch];
-    for (int b = 0; b < n_seq; ++b) {
-        const int lo = shape.window > 0 ? std::max(0, meta.pos[b] - shape.window + 1) : 0;
-        int n = meta.pos[b] / kTileKeys - lo / kTileKeys + 1;
-        if (world > 1) n = (n + world - 1) / world + 1;
-        seq_tile_count[b] = n;
-        max_tiles = std::max(max_tiles, n);
-        total_tiles += n;
-    }
-    const size_t rows = size_t(n_seq) * shape.q_heads;
-    if (rows * max_tiles * shape.head_dim > ws.part_o_floats || rows * max_tiles * 2 > ws.part_ml_floats) {
-        return fail(HC_KV_OVERFLOW, "decode: the split-attention workspace is too small for this call");
-    }
     TcArgs args{};
-    args.q = q;
+    fill_common_args(args, ctx, shape, cache, q, ws, ep);
     args.tokens = n_seq;
-    args.q_heads = shape.q_heads;
-    args.kv_heads = shape.kv_heads;
-    int log_group = 0;
-    while ((1 << log_group) < shape.group) ++log_group;
-    args.log_group = log_group;
-    args.window = shape.window;
-    args.c = shape.c;
-    args.sinks = shape.sinks;
-    args.count_sink = shape.count_sink;
-    args.map = cache.map;
-    args.ep = ep;
-    args.status = ctx->status_dev;
     args.decode = 1;
-    // Items of consecutive tiles, about six per CTA so that the static round-robin balances (measured
-    // best of 3 .. 12 on uniform and ragged batches).  The head_dim 256 kernel does not look ahead
-    // across items: about one item per CTA.
-    const long long items_per_sm = shape.head_dim == 256 ? 1LL : 6LL;
-    const long long target = items_per_sm * std::max(ctx->sm_count, 1);
-    long long per = (total_tiles * shape.kv_heads + target - 1) / target;
-    args.tiles_per_item = int(std::min<long long>(std::max<long long>(per, 1), 64));
-    args.part_o = ws.part_o;
-    args.part_ml = ws.part_ml;
-    args.part_tiles = max_tiles;
     args.meta = meta;
-    args.chunks = (max_tiles + args.tiles_per_item - 1) / args.tiles_per_item;
-    args.n_items = args.chunks * shape.kv_heads * n_seq;
-    if (world <= 1) {
-        // Per-sequence item lists: each sequence's tiles in runs of one size, about `tiles_per_item`.
-        args.per_seq = 1;
-        int next = 0;
-        for (int b = 0; b < n_seq; ++b) {
-            const int tiles = std::max(seq_tile_count[b], 1);
-            const int want = (tiles + args.tiles_per_item - 1) / args.tiles_per_item;
-            const int run = (tiles + want - 1) / want;               // tiles per run, balanced
-            const int chunks = (tiles + run - 1) / run;              // no empty run
-            args.item_start[b] = next;
-            args.seq_chunks[b] = static_cast<unsigned short>(chunks);
-            args.seq_tiles[b] = static_cast<unsigned short>(run);
-            args.seq_magic[b] = division_magic(uint32_t(chunks), uint32_t(chunks) * uint32_t(shape.kv_heads));
-            next += chunks * shape.kv_heads;
-        }
-        for (int b = n_seq; b <= kMaxBatch; ++b) args.item_start[b] = next;
-        args.n_items = next;
+    const DecodePlan plan = tc_plan_decode(ctx, shape, cache.map, meta, n_seq, ws.part_o_floats);
+    args.finish = plan.finish;
+    args.log_run = plan.log_run;
+    args.tile_partials = plan.tile_partials;
+    args.slots = plan.slots;
+    // One item per (sequence, kv head, run of the sequence's visible key tiles).
+    int next = 0;
+    for (int b = 0; b < n_seq; ++b) {
+        const int n = plan.finish ? 1 : visible_groups(meta.pos[b], meta.pos[b], shape.window, plan.log_run);
+        args.item_start[b] = next;
+        args.seq_slots[b] = static_cast<unsigned short>(n);
+        args.seq_magic[b] = division_magic(uint32_t(n), uint32_t(n) * uint32_t(shape.kv_heads));
+        next += n * shape.kv_heads;
     }
-    args.magic_chunks = division_magic(uint32_t(args.chunks), uint32_t(args.n_items));
-    args.magic_kv_heads = division_magic(uint32_t(shape.kv_heads), uint32_t(args.n_items));
-    args.magic_world = division_magic(uint32_t(std::max(cache.map.world, 1)), 1u << 24);
-    hc_status st = shape.head_dim == 64 ? launch_tc<64>(ctx, args, layer, stream)
-                   : shape.head_dim == 128 ? launch_tc<128>(ctx, args, layer, stream)
-                   : launch_tc256(ctx, layer.tmap_k, layer.tmap_v, &args, args.n_items, stream);
-    if (st != HC_OK) return st;
-    return launch_merge(ctx, shape, meta, n_seq, ws, max_tiles, world, cache.map.rank, ep, stream);
+    for (int b = n_seq; b <= kMaxBatch; ++b) args.item_start[b] = next;
+    args.n_items = next;
+    if (!args.finish) {
+        const size_t rows = size_t(n_seq) * shape.q_heads;
+        if (rows * plan.slots * shape.head_dim > ws.part_o_floats || rows * plan.slots * 2 > ws.part_ml_floats) {
+            return fail(HC_KV_OVERFLOW, "decode: the split-attention workspace is too small for this call");
+        }
+    }
+    const hc_status st = launch_any(ctx, shape, args, layer, stream);
+    if (st != HC_OK || args.finish) return st;
+    return launch_merge_decode(ctx, shape, cache.map, meta, n_seq, ws, plan, ep, stream);
 }
-
 
 }  // namespace hc

@@ -37,11 +37,17 @@ struct Tc256Barriers {
     int abort_flag;
     float mm[4][kRows];
     float l[4][kRows];
+    float m2[2][kRows], l2[2][kRows];   // the rows' second fold between segments, per half
 };
 
+// MODE says what becomes of an item's rows (TcArgs: finish, tile_partials), so that a launch carries
+// the code of its own way only: 0 = the kernel finishes them, 1 = segment partials, 2 = tile partials.
+template <int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                        const TcArgs args) {
+    constexpr bool kFinish = MODE == 0;
+    constexpr bool kTilePartials = MODE == 2;
     extern __shared__ unsigned char raw_smem[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
     unsigned char* q_smem = base;
@@ -290,6 +296,22 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         const int g = row & (G - 1);
         const uint32_t lane_base = uint32_t(quad * 32) << 16;
         const uint32_t o_tmem = tmem + lane_base + kOCol256 + half * 128;
+        auto state_of_row = [&]() -> float* {
+            return args.row_state + size_t(blockIdx.x) * (kD * kRows) + size_t(half * 128) * kRows + row;
+        };
+        // (M, L) the second fold stands at: what the last segment end left, or the seed.
+        auto second_fold_state = [&](bool state_holds, uint16_t sink, float& M2, float& L2) {
+            if (state_holds) {
+                M2 = bars->m2[half][row];
+                L2 = bars->l2[half][row];
+            } else if (args.count_sink) {
+                M2 = __fmul_rn(bf16_bits_to_float(sink), kLog2e);
+                L2 = 1.0f;
+            } else {
+                M2 = kEmptyMax;
+                L2 = 0.0f;
+            }
+        };
         auto stage_q = [&](const TcItem& w) {
             const bool valid = t_local < w.valid_tokens;
             const uint16_t* src = args.q + (size_t(w.row0 + t_local) * args.q_heads + size_t(w.kv_head) * G + g) * kD;
@@ -312,8 +334,8 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         bool ok = true;
         TcItemIter walk = items_begin(args);
         if (half == 0 && walk.item < args.n_items) stage_q(walk.w);
-        // The head's sink is fetched one item ahead (prefill only: decode writes raw partials).
-        const bool wants_sink = args.count_sink && args.sinks != nullptr && !args.decode;
+        // The head's sink is fetched one item ahead (only when this kernel runs the second fold).
+        const bool wants_sink = kFinish && args.count_sink && args.sinks != nullptr;
         uint16_t sink_bits = kNoSinkBits;
         if (wants_sink && walk.item < args.n_items) sink_bits = args.sinks[walk.w.kv_head * G + g];
         while (ok && walk.item < args.n_items) {
@@ -322,56 +344,37 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
             const int head = w.kv_head * G + g;
             const bool valid = t_local < w.valid_tokens;
             const bool warp_has_rows = quad * 32 < (w.valid_tokens << args.log_group);
-            float M, L;
-            if (args.count_sink) {
-                M = __fmul_rn(bf16_bits_to_float(sink_bits), kLog2e);
-                L = 1.0f;
-            } else {
-                M = kEmptyMax;
-                L = 0.0f;
-            }
+            const uint16_t item_sink = sink_bits;
             if (wants_sink && walk.item < args.n_items) sink_bits = args.sinks[walk.w.kv_head * G + g];
-            float A[128];
-            #pragma unroll
-            for (int i = 0; i < 128; ++i) A[i] = 0.0f;
-            for (int j = 0; j < w.n_tiles; ++j, ++t) {
+            // Half 0 also stages the next item's Q tile once this item's last S has been issued.
+            auto stage_next_q = [&](int j) -> bool {
                 if (half == 0 && j == w.n_tiles - 1 && walk.item < args.n_items) {
-                    // The item's last S has been issued: its Q tile is free for the next item's.
-                    if (!mbar_wait(&bars->q_empty, it & 1, abort_flag, args.status, 10)) { ok = false; break; }
+                    if (!mbar_wait(&bars->q_empty, it & 1, abort_flag, args.status, 10)) return false;
                     stage_q(walk.w);
                 }
-                if (!mbar_wait(&bars->o_full, t & 1, abort_flag, args.status, 9)) { ok = false; break; }
-                tc_fence_after();
-                if (!warp_has_rows) {
-                    tc_fence_before();
-                    mbar_arrive(&bars->o_free);
-                    continue;
-                }
-                const float mm_tile = bars->mm[t & 3][row];
-                const float l_tile = bars->l[t & 3][row];
-                float Mn = 0.0f, a = 1.0f, b = 1.0f;
-                size_t prow = 0;
-                if (args.decode) {
-                    prow = (size_t(w.row0) * args.q_heads + head) * args.part_tiles + (w.ordinal0 + j);
-                    if (valid && half == 0) {
-                        args.part_ml[prow * 2] = mm_tile;
-                        args.part_ml[prow * 2 + 1] = l_tile;
-                    }
-                } else {
-                    fold_coefficients(M, mm_tile, Mn, a, b);
-                    L = __fmaf_rn(L, a, __fmul_rn(l_tile, b));
-                    M = Mn;
-                }
-                #pragma unroll
-                for (int chunk = 0; chunk < 4; ++chunk) {
-                    uint32_t o[32];
-                    HC_TMEM_LD32(o_tmem + chunk * 32, o);
-                    tc_wait_ld();
-                    if (chunk == 3) {
+                return true;
+            };
+            if constexpr (kTilePartials) {
+                // Finely split decode: every tile's own partial goes to the workspace, both folds to the merge.
+                for (int j = 0; j < w.n_tiles; ++j, ++t) {
+                    if (!stage_next_q(j)) { ok = false; break; }
+                    if (!mbar_wait(&bars->o_full, t & 1, abort_flag, args.status, 9)) { ok = false; break; }
+                    tc_fence_after();
+                    if (!warp_has_rows) {
                         tc_fence_before();
                         mbar_arrive(&bars->o_free);
+                        continue;
                     }
-                    if (args.decode) {
+                    const size_t prow = (size_t(w.row0) * args.q_heads + head) * args.slots + (w.slot + j);
+                    #pragma unroll
+                    for (int chunk = 0; chunk < 4; ++chunk) {
+                        uint32_t o[32];
+                        HC_TMEM_LD32(o_tmem + chunk * 32, o);
+                        tc_wait_ld();
+                        if (chunk == 3) {
+                            tc_fence_before();
+                            mbar_arrive(&bars->o_free);
+                        }
                         if (valid) {
                             float* dst = args.part_o + prow * kD + half * 128 + chunk * 32;
                             #pragma unroll
@@ -379,18 +382,142 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
                                 *reinterpret_cast<uint4*>(dst + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
                             }
                         }
-                    } else {
+                    }
+                    if (valid && half == 0) {
+                        *reinterpret_cast<float2*>(args.part_ml + prow * 2) = make_float2(bars->mm[t & 3][row], bars->l[t & 3][row]);
+                    }
+                }
+                if (!ok) break;
+                ++it;
+                continue;
+            }
+            // The running segment's partial: a fold over its tiles from the empty state (both halves of
+            // the row carry M and L, the same chain, the same bits).
+            float M = kEmptyMax, L = 0.0f;
+            float A[128];
+            #pragma unroll
+            for (int i = 0; i < 128; ++i) A[i] = 0.0f;
+            // One pass per segment the item touches.  With finish, the row's second fold runs between
+            // the passes.  Its state is kept out of the registers: (M2, L2) in shared memory (one copy per
+            // half), the values in global memory (element i of this thread's half row at
+            // state[i * kRows]); both are untouched until the item's first segment is complete, which
+            // a tile's segment index tells.
+            for (int j = 0; ok && j < w.n_tiles;) {
+                const int pass_tile = w.tile_first + j * world;
+                const int pass_last = (((pass_tile >> args.map.log_segment) + 1) << args.map.log_segment) - 1;
+                const int pass_end = min(w.n_tiles, j + (pass_last - pass_tile) / world + 1);
+                // The first fold over the segment's tiles.
+                for (; j < pass_end; ++j, ++t) {
+                    if (!stage_next_q(j)) { ok = false; break; }
+                    if (!mbar_wait(&bars->o_full, t & 1, abort_flag, args.status, 9)) { ok = false; break; }
+                    tc_fence_after();
+                    if (!warp_has_rows) {
+                        tc_fence_before();
+                        mbar_arrive(&bars->o_free);
+                        continue;
+                    }
+                    float Mn, a, b;
+                    fold_coefficients(M, bars->mm[t & 3][row], Mn, a, b);
+                    L = __fmaf_rn(L, a, __fmul_rn(bars->l[t & 3][row], b));
+                    M = Mn;
+                    #pragma unroll
+                    for (int chunk = 0; chunk < 4; ++chunk) {
+                        uint32_t o[32];
+                        HC_TMEM_LD32(o_tmem + chunk * 32, o);
+                        tc_wait_ld();
+                        if (chunk == 3) {
+                            tc_fence_before();
+                            mbar_arrive(&bars->o_free);
+                        }
                         #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
                             fold_value2(A[chunk * 32 + i], A[chunk * 32 + i + 1], a, o[i], o[i + 1], b);
                         }
                     }
                 }
+                if constexpr (!kFinish) {
+                    // The segment's partial goes to the workspace (a merge kernel runs the second fold), and
+                    // the next segment of the run starts over.
+                    if (ok && valid) {
+                        const int slot = (pass_tile >> args.map.log_segment) - w.first_segment;
+                        const size_t prow = ((size_t(w.row0 + t_local)) * args.q_heads + head) * args.slots + slot;
+                        float* dst = args.part_o + prow * kD + half * 128;
+                        #pragma unroll
+                        for (int i = 0; i < 128; i += 4) {
+                            *reinterpret_cast<float4*>(dst + i) = make_float4(A[i], A[i + 1], A[i + 2], A[i + 3]);
+                        }
+                        if (half == 0) *reinterpret_cast<float2*>(args.part_ml + prow * 2) = make_float2(M, L);
+                    }
+                    if (j < w.n_tiles) {
+                        #pragma unroll
+                        for (int i = 0; i < 128; ++i) A[i] = 0.0f;
+                        M = kEmptyMax;
+                        L = 0.0f;
+                    }
+                }
+                if (kFinish && ok && warp_has_rows && j < w.n_tiles) {
+                    // A segment is complete and another follows: fold it into the row's state and start over.
+                    const int tile = w.tile_first + (j - 1) * world;
+                    const bool state_holds = (tile >> args.map.log_segment) != (w.tile_first >> args.map.log_segment);
+                    float M2, L2;
+                    second_fold_state(state_holds, item_sink, M2, L2);
+                    float Mn2, a2, b2;
+                    fold_coefficients(M2, M, Mn2, a2, b2);
+                    bars->m2[half][row] = Mn2;
+                    bars->l2[half][row] = __fmaf_rn(L2, a2, __fmul_rn(L, b2));
+                    float* const state = state_of_row();
+                    #pragma unroll
+                    for (int i0 = 0; i0 < 128; i0 += 16) {
+                        float before[16];
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) before[i] = state_holds ? state[(i0 + i) * kRows] : 0.0f;
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            state[(i0 + i) * kRows] = fold_value(before[i], a2, A[i0 + i], b2);
+                            A[i0 + i] = 0.0f;
+                        }
+                        asm volatile("" ::: "memory");      // sixteen values in flight, not all of them
+                    }
+                    M = kEmptyMax;
+                    L = 0.0f;
+                }
             }
             if (!ok) break;
-            if (valid && !args.decode) {
-                const size_t out_row = size_t(w.row0 + t_local);
-                const int col0 = half * 128;
+            const size_t out_row = size_t(w.row0 + t_local);
+            const int col0 = half * 128;
+            if constexpr (!kFinish) {
+                ++it;
+                continue;
+            }
+            // The row's last segment: the last step of the second fold, which started from the sink (or
+            // from the empty state).
+            {
+                const int last_tile = w.tile_first + (w.n_tiles - 1) * world;
+                const bool state_holds = warp_has_rows && (last_tile >> args.map.log_segment) != (w.tile_first >> args.map.log_segment);
+                float M2, L2;
+                second_fold_state(state_holds, item_sink, M2, L2);
+                float Mn, a, b;
+                fold_coefficients(M2, M, Mn, a, b);
+                L = __fmaf_rn(L2, a, __fmul_rn(L, b));
+                M = Mn;
+                const float* const state = state_of_row();
+                if (state_holds) {
+                    #pragma unroll
+                    for (int i0 = 0; i0 < 128; i0 += 16) {
+                        float before[16];
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) before[i] = state[(i0 + i) * kRows];
+                        #pragma unroll
+                        for (int i = 0; i < 16; ++i) A[i0 + i] = fold_value(before[i], a, A[i0 + i], b);
+                        asm volatile("" ::: "memory");
+                    }
+                } else {
+                    // fold_value(0, a, A, b) = 0 * a + A * b = A * b exactly: one multiply.
+                    #pragma unroll
+                    for (int i = 0; i < 128; ++i) A[i] = __fmul_rn(A[i], b);
+                }
+            }
+            if (valid) {
                 if (args.ep.write_partial) {
                     float* dst = reinterpret_cast<float*>(args.ep.out) + (out_row * args.q_heads + head) * size_t(kD + 2) + col0;
                     #pragma unroll
@@ -449,14 +576,16 @@ hc_status launch_tc256(hc_context* ctx, const void* tmap_k, const void* tmap_v, 
                        int n_items, cudaStream_t stream) {
     const TcArgs& args = *static_cast<const TcArgs*>(args_ptr);
     const int smem = 1024 + kQBytes256 + 2 * kTileBytes256 + int(sizeof(Tc256Barriers));
-    static bool configured[64] = {};
-    if (!configured[ctx->device & 63]) {
-        cudaError_t err = cudaFuncSetAttribute(attention_tc256_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    auto kernel = args.finish ? attention_tc256_kernel<0> : args.tile_partials ? attention_tc256_kernel<2> : attention_tc256_kernel<1>;
+    static bool configured[64][3] = {};
+    const int mode = args.finish ? 0 : args.tile_partials ? 2 : 1;
+    if (!configured[ctx->device & 63][mode]) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (err != cudaSuccess) return check_cuda(err, "attention_tc256_kernel shared memory");
-        configured[ctx->device & 63] = true;
+        configured[ctx->device & 63][mode] = true;
     }
     const int grid = std::max(1, std::min(n_items, std::max(ctx->sm_count, 1)));
-    const cudaError_t launched = launch_pdl(attention_tc256_kernel, grid, kTcThreads, size_t(smem), stream,
+    const cudaError_t launched = launch_pdl(kernel, grid, kTcThreads, size_t(smem), stream,
                                             *static_cast<const CUtensorMap*>(tmap_k),
                                             *static_cast<const CUtensorMap*>(tmap_v), args);
     ctx->launches += 1;

@@ -14,17 +14,30 @@
 //       p_k  = bf16( exp2( fma(s_k, c, -(m * c)) ) ) for visible k, 0 otherwise;  c = sm_scale * log2(e)
 //       l    = sum_k p_k ,  O = sum_k p_k V_k                              (fp32)
 //       mm   = m * c
-//   the row's result is a left fold over its tiles in ascending order, seeded with the sink:
-//       (M, L, A) = (sink * log2(e), 1, 0)             -- "no sink" is sink = bf16(-1e30)
+//   tiles are grouped into segments of 2^log_segment consecutive tiles, absolute like the tiles
+//   (1024 or 4096 keys; a property of the layer, fixed when its cache is created).  A segment's
+//   partial is a left fold over its tiles that hold a visible key, in ascending order, from the
+//   empty state:
+//       (M, L, A) = (-1e30, 0, 0)
 //       Mn = max(M, mm); a = exp2(M - Mn); b = exp2(mm - Mn)
 //       L = fma(L, a, l * b);  A = fma(A, a, O * b);  M = Mn
+//   and the row's result is the same fold over its segments' partials (M, L, A) in ascending
+//   order, seeded with the sink:
+//       (M, L, A) = (sink * log2(e), 1, 0)             -- "no sink" is sink = bf16(-1e30)
 //       out = A / L, then * sigmoid(gate) when gated.
+//   Folding an empty partial changes nothing, exactly, so it does not matter whether a kernel
+//   visits a segment in which a row sees no key.
 //
 // Seeding with the sink is the reference's own construction
 // (Sources/HydraMetal/Shaders/attention.metal:156-165): the sink adds to the denominator only.
 // A tile partial does not depend on which kernel, which chunk or which split produced it, and the
-// fold visits tiles in the same order everywhere, so chunked prefill, token-by-token decode and
-// split decode give the same bits as long as they share the tile-partial routine.
+// two folds visit tiles and segments in the same order everywhere.  So the work of a row may be cut
+// anywhere without changing a bit of the result: a thread block may take the whole row and run both
+// folds, or one segment and leave the second fold to a merge kernel, or a few tiles and leave both
+// folds to it; chunked prefill, token-by-token decode and every such split agree as long as they
+// share the tile-partial routine.  Small segments are what lets a prefill launch with few rows
+// spread one row's keys over several thread blocks at little cost in partials; large segments keep
+// the second fold rare where whole rows already fill the machine.
 #pragma once
 
 #include <cuda_bf16.h>
@@ -104,15 +117,21 @@ __device__ __forceinline__ void store_io(void* base, size_t index, int dtype, fl
     else reinterpret_cast<uint16_t*>(base)[index] = float_to_bf16_bits(value);
 }
 
-// Where position `pos` of a sequence lives inside one head's rows of the cache.
+// Where position `pos` of a sequence lives inside one head's rows of the cache, and how the layer
+// groups its key tiles into segments.
 //   ring > 0            : physical = pos % ring                      (ring is a multiple of 128)
 //   world > 1 (sequence): tile j = pos / 128 belongs to rank j % world and is that rank's local
 //                         tile j / world
+//   log_segment         : a segment is 2^log_segment consecutive tiles, absolute like the tiles
+//                         (3 or 5: 1024 or 4096 keys; fixed per layer when the cache is created)
 struct RowMap {
     int ring;
     int rank;
     int world;
+    int log_segment;
 };
+constexpr int kLogSegmentSmall = 3;        // layers whose prefill launches need their rows' keys split
+constexpr int kLogSegmentLarge = 5;        // all others
 __host__ __device__ __forceinline__ bool row_is_local(const RowMap& map, int pos) {
     return map.world <= 1 || ((pos / kTileKeys) % map.world) == map.rank;
 }
@@ -120,6 +139,43 @@ __host__ __device__ __forceinline__ int row_of_position(const RowMap& map, int p
     if (map.world > 1) return ((pos / kTileKeys) / map.world) * kTileKeys + (pos % kTileKeys);
     return map.ring > 0 ? pos % map.ring : pos;
 }
+// Key tiles are handed out in aligned groups of 2^log_tiles consecutive tiles: the layer's segments
+// (log_tiles = map.log_segment) or shorter runs inside them.  group_tiles gives the tiles of one
+// group that a block of queries at positions [first_pos, last_pos] attends to on this rank;
+// `ordinal` counts from the block's first visible group.  The result is the first tile and the number
+// of tiles (`world` apart); a count <= 0 means nothing to do.  Every kernel that produces or merges
+// partials derives its work from these functions.
+struct TileRange {
+    int first;
+    int count;
+};
+__host__ __device__ __forceinline__ int first_visible_tile(int first_pos, int window) {
+    return (window > 0 ? (first_pos - window + 1 > 0 ? first_pos - window + 1 : 0) : 0) / kTileKeys;
+}
+__host__ __device__ __forceinline__ int visible_groups(int first_pos, int last_pos, int window, int log_tiles) {
+    return ((last_pos / kTileKeys) >> log_tiles) - (first_visible_tile(first_pos, window) >> log_tiles) + 1;
+}
+__host__ __device__ __forceinline__ TileRange owned_tiles(const RowMap& map, int t0, int t1) {
+    const int world = map.world > 1 ? map.world : 1;
+    if (world > 1) t0 += ((map.rank - t0 % world) + world) % world;
+    TileRange out;
+    out.first = t0;
+    out.count = t0 > t1 ? 0 : (t1 - t0) / world + 1;
+    return out;
+}
+__host__ __device__ __forceinline__ TileRange group_tiles(const RowMap& map, int first_pos, int last_pos, int window,
+                                                         int ordinal, int log_tiles) {
+    const int tile_lo = first_visible_tile(first_pos, window);
+    const int tile_hi = last_pos / kTileKeys;
+    const int group = (tile_lo >> log_tiles) + ordinal;
+    const int g0 = group << log_tiles, g1 = g0 + (1 << log_tiles) - 1;
+    return owned_tiles(map, g0 > tile_lo ? g0 : tile_lo, g1 < tile_hi ? g1 : tile_hi);
+}
+// All the key tiles of this rank that rows at positions first_pos..last_pos see.
+__host__ __device__ __forceinline__ TileRange row_tiles(const RowMap& map, int first_pos, int last_pos, int window) {
+    return owned_tiles(map, first_visible_tile(first_pos, window), last_pos / kTileKeys);
+}
+
 // First physical row of absolute tile j (callers only ask for tiles they own).
 __host__ __device__ __forceinline__ int row_of_tile(const RowMap& map, int tile) {
     return row_of_position(map, tile * kTileKeys);

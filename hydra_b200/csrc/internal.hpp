@@ -98,8 +98,8 @@ struct EpilogueArgs {
 struct Workspace {
     uint16_t* qprep = nullptr;   // bf16 [qprep_tokens][q_heads][d]
     int qprep_tokens = 0;
-    float* part_o = nullptr;     // fp32 [rows][tiles][d], rows and tiles those of the call
-    float* part_ml = nullptr;    // fp32 [rows][tiles][2]
+    float* part_o = nullptr;     // fp32 [rows][slots][d]: segment partials, rows and slots those of the call
+    float* part_ml = nullptr;    // fp32 [rows][slots][2]
     size_t part_o_floats = 0;    // capacities
     size_t part_ml_floats = 0;
 };
@@ -129,6 +129,7 @@ struct hc_layer_store {
     uint16_t* v = nullptr;
     int ring = 0;
     int capacity = 0;
+    int log_segment = 0;          // key tiles per segment, as a power of two (see common.cuh)
     bool keeps_history = false;
     void* tmap_k = nullptr;       // tensor maps of the tcgen05 path (host copies), or null
     void* tmap_v = nullptr;
@@ -175,9 +176,29 @@ hc_status simt_prefill(hc_context* ctx, const AttnShape& shape, const CacheView&
 hc_status simt_decode(hc_context* ctx, const AttnShape& shape, const CacheView& cache,
                       const BatchMeta& meta, int n_seq, const uint16_t* q, const Workspace& ws,
                       const EpilogueArgs& ep, cudaStream_t stream);
-hc_status launch_merge(hc_context* ctx, const AttnShape& shape, const BatchMeta& meta, int n_seq,
-                       const Workspace& ws, int part_tiles, int world, int rank, const EpilogueArgs& ep,
-                       cudaStream_t stream);
+// How a decode launch cuts its rows' keys (see TcArgs in tc_common.cuh for the three ways).
+struct DecodePlan {
+    int finish;          // whole rows per item, finished by the kernel itself
+    int log_run;         // otherwise: items are aligned runs of 2^log_run tiles
+    int tile_partials;   // the kernel writes one partial per tile (log_run < log_segment) rather than per segment
+    int slots;           // partial slots per row
+    int tiles;           // key tiles of the longest row (on this rank)
+};
+// The coarsest cut that gives at least target_items items, runs of 2^max_log_run tiles at most.
+DecodePlan plan_decode(const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq, int target_items,
+                       bool allow_whole, int max_log_run);
+// The cuts simt_decode and tc_decode make (the latter given the room for partials or row state).
+DecodePlan simt_plan_decode(const hc_context* ctx, const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq);
+DecodePlan tc_plan_decode(const hc_context* ctx, const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq,
+                          size_t part_o_floats);
+// Both folds (tile partials) or the second fold (segment partials) over the partials in `ws`, then the
+// epilogue: for the rows of a decode batch, or for the query tokens of a prefill chunk.
+hc_status launch_merge_decode(hc_context* ctx, const AttnShape& shape, const RowMap& map, const BatchMeta& meta,
+                              int n_seq, const Workspace& ws, const DecodePlan& plan, const EpilogueArgs& ep,
+                              cudaStream_t stream);
+hc_status launch_merge_prefill(hc_context* ctx, const AttnShape& shape, const RowMap& map, int tokens,
+                               int first_position, const Workspace& ws, int slots, const EpilogueArgs& ep,
+                               cudaStream_t stream);
 hc_status launch_combine(hc_context* ctx, const float* gathered, int world, int rows, int q_heads,
                          int d, const EpilogueArgs& ep, cudaStream_t stream);
 // Device address of the fixed scratch array on `device` (which must be current).
@@ -187,7 +208,7 @@ hc_status static_scratch_prepare(int device, float** address);
 bool tc_supported(const AttnShape& shape);
 hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer,
                      const CacheView& cache, int seq, const uint16_t* q, int tokens,
-                     int first_position, const EpilogueArgs& ep, cudaStream_t stream);
+                     int first_position, const Workspace& ws, const EpilogueArgs& ep, cudaStream_t stream);
 hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer,
                     const CacheView& cache, const BatchMeta& meta, int n_seq, const uint16_t* q,
                     const Workspace& ws, const EpilogueArgs& ep, cudaStream_t stream);

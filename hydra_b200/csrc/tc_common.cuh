@@ -10,7 +10,7 @@ namespace {
 
 struct TcArgs {
     const uint16_t* q;        // bf16 [rows][q_heads][d], prepared
-    int tokens;               // prefill: tokens of the chunk
+    int tokens;               // prefill: tokens of the chunk; decode: batch entries
     int first_position;
     int q_heads;
     int kv_heads;
@@ -25,25 +25,30 @@ struct TcArgs {
     int* status;
     int n_items;              // work items in the list
     int mtiles;               // prefill: row tiles per kv head
-    // Decode (split over key tiles): one query token per batch entry; an item is a run of
-    // `tiles_per_item` consecutive key tiles of one (sequence, kv head) whose partials it writes.
+    // How a launch cuts its rows' keys into items (the bits are the same whichever the host picks):
+    //   finish != 0       an item is all the key tiles of one row tile and kv head (prefill) or of one
+    //                     sequence and kv head (decode).  The kernel runs both folds and the epilogue,
+    //                     keeping the second fold's values between segments in row_state.
+    //   otherwise         an item is an aligned run of 2^log_run tiles of those rows and the kernel writes
+    //                     partials to the workspace, `slots` per row at most: with tile_partials == 0
+    //                     (log_run >= map.log_segment: whole segments) each segment's partial, slot =
+    //                     ordinal of the segment; with tile_partials != 0 (decode only, log_run <
+    //                     map.log_segment) every tile's own partial, slot = ordinal of the tile among
+    //                     the row's tiles.  A merge kernel finishes the rows.
     int decode;
-    int chunks;               // decode: items per (sequence, kv head)
-    int tiles_per_item;
-    float* part_o;            // fp32 [rows][part_tiles][d]
-    float* part_ml;           // fp32 [rows][part_tiles][2]
-    int part_tiles;
+    int slots;
+    int finish;
+    int log_run;
+    int tile_partials;
+    float* part_o;            // fp32 [rows][slots][d]
+    float* part_ml;           // fp32 [rows][slots][2]
+    float* row_state;         // fp32 [thread blocks][d][128], finish only
     // Multipliers for the divisions of decode_item (see fast_div); 0 = divide the ordinary way.
-    uint32_t magic_chunks, magic_kv_heads, magic_world;
-    // Decode, per-sequence item lists (per_seq != 0; used when the cache is not sequence-sharded):
-    // sequence b's key tiles are cut into seq_chunks[b] runs of seq_tiles[b] tiles (the last one may
-    // be shorter, never empty), so ragged batches leave no empty items and the runs of one sequence
-    // are of one size.  Its items, kv head major, start at item_start[b].
-    int per_seq;
+    uint32_t magic_slots, magic_kv_heads;
+    // Decode: sequence b has seq_slots[b] runs; its items, kv head major, start at item_start[b].
     int item_start[kMaxBatch + 1];
-    unsigned short seq_chunks[kMaxBatch];
-    unsigned short seq_tiles[kMaxBatch];
-    uint32_t seq_magic[kMaxBatch];       // division by seq_chunks[b]
+    unsigned short seq_slots[kMaxBatch];
+    uint32_t seq_magic[kMaxBatch];       // division by seq_slots[b]
     BatchMeta meta;
 };
 
@@ -66,42 +71,36 @@ struct TcItem {
     int first_pos;     // position of the first query token
     int tile_first;    // absolute index of the first key tile
     int n_tiles;       // key tiles to visit (stride `world` apart); <= 0: nothing to do
-    int ordinal0;      // decode: ordinal of the first tile among the row's tiles
+    int slot;          // ordinal of the item's run among the rows' runs; with tile partials, the row's
+                       // partial slot of the item's first tile
+    int first_segment; // absolute index of the first segment the rows see (segment partials go to
+                       // slot = segment - first_segment)
 };
 
 __device__ __forceinline__ TcItem decode_item(const TcArgs& args, int index) {
     TcItem w;
     const int tokens_per_tile = kRows >> args.log_group;
-    int chunk = 0;
-    int tiles_per_item = args.tiles_per_item;
     if (args.decode) {
-        int b;
-        if (args.per_seq) {
-            int lo = 0, hi = args.tokens;                 // item_start[lo] <= index < item_start[hi]
-            while (hi - lo > 1) {
-                const int mid = (lo + hi) >> 1;
-                if (index >= args.item_start[mid]) lo = mid; else hi = mid;
-            }
-            b = lo;
-            const int local = index - args.item_start[b];
-            const int chunks = args.seq_chunks[b];
-            w.kv_head = fast_div(local, chunks, args.seq_magic[b]);
-            chunk = local - w.kv_head * chunks;
-            tiles_per_item = args.seq_tiles[b];
-        } else {
-            const int rest = fast_div(index, args.chunks, args.magic_chunks);
-            chunk = index - rest * args.chunks;
-            b = fast_div(rest, args.kv_heads, args.magic_kv_heads);
-            w.kv_head = rest - b * args.kv_heads;
+        int lo = 0, hi = args.tokens;                 // item_start[lo] <= index < item_start[hi]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (index >= args.item_start[mid]) lo = mid; else hi = mid;
         }
+        const int b = lo;
+        const int local = index - args.item_start[b];
+        const int slots = args.seq_slots[b];
+        w.kv_head = fast_div(local, slots, args.seq_magic[b]);
+        w.slot = local - w.kv_head * slots;
         w.row0 = b;
         w.valid_tokens = 1;
         w.first_pos = args.meta.pos[b];
         w.seq = args.meta.seq[b];
     } else {
-        // Longest key ranges first: descending row tile, the kv heads of one row tile adjacent.
-        const int tile_index = fast_div(index, args.kv_heads, args.magic_kv_heads);
-        w.kv_head = index - tile_index * args.kv_heads;
+        // Longest key ranges first: descending row tile; a row tile's segments and kv heads adjacent.
+        const int rest = fast_div(index, args.slots, args.magic_slots);
+        w.slot = index - rest * args.slots;
+        const int tile_index = fast_div(rest, args.kv_heads, args.magic_kv_heads);
+        w.kv_head = rest - tile_index * args.kv_heads;
         const int mtile = args.mtiles - 1 - tile_index;
         w.row0 = mtile * tokens_per_tile;
         w.valid_tokens = min(tokens_per_tile, args.tokens - w.row0);
@@ -109,21 +108,15 @@ __device__ __forceinline__ TcItem decode_item(const TcArgs& args, int index) {
         w.seq = args.seq;
     }
     const int last_pos = w.first_pos + w.valid_tokens - 1;
-    const int lo_first = args.window > 0 ? max(0, w.first_pos - args.window + 1) : 0;
-    const int world = max(args.map.world, 1);
-    int tile_first = lo_first / kTileKeys;
-    const int tile_last = last_pos / kTileKeys;
-    if (world > 1) tile_first += ((args.map.rank - tile_first % world) + world) % world;
-    int n_tiles = tile_first > tile_last ? 0
-                  : (world > 1 ? fast_div(tile_last - tile_first, world, args.magic_world) : tile_last - tile_first) + 1;
-    w.ordinal0 = 0;
-    if (args.decode) {
-        w.ordinal0 = chunk * tiles_per_item;
-        tile_first += w.ordinal0 * world;
-        n_tiles = min(tiles_per_item, n_tiles - w.ordinal0);
+    const TileRange tiles = args.finish ? row_tiles(args.map, w.first_pos, last_pos, args.window)
+                                        : group_tiles(args.map, w.first_pos, last_pos, args.window, w.slot, args.log_run);
+    w.tile_first = tiles.first;
+    w.n_tiles = tiles.count;
+    w.first_segment = first_visible_tile(w.first_pos, args.window) >> args.map.log_segment;
+    if (args.tile_partials && tiles.count > 0) {
+        const int world = args.map.world > 1 ? args.map.world : 1;
+        w.slot = (tiles.first - row_tiles(args.map, w.first_pos, last_pos, args.window).first) / world;
     }
-    w.tile_first = tile_first;
-    w.n_tiles = n_tiles;
     return w;
 }
 

@@ -63,11 +63,12 @@ def test_static_decode_refusals():
     import dataclasses
     import hydra_b200 as hb
     ctx = hb.Context(0)
-    # beyond the fixed array: refused with a message that states the sizes
-    big = tl.Layer(hb, ctx, 64, 8, 256, 16384, max_seqs=8)
-    qd = tl.device_empty((8, 64, 256))
+    # beyond the fixed array: refused with a message that states the sizes.  Two long sequences are few
+    # enough that the library cuts them tile by tile: 128 rows x 128 tile partials of 258 floats.
+    big = tl.Layer(hb, ctx, 64, 8, 256, 16384, max_seqs=2)
+    qd = tl.device_empty((2, 64, 256))
     with pytest.raises(hb.CacheOverflow) as info:
-        big.backend.attention_static(big.cache, 0, qd, qd, [16383] * 8, big.params, seq_ids=list(range(8)))
+        big.backend.attention_static(big.cache, 0, qd, qd, [16383] * 2, big.params, seq_ids=[0, 1])
     assert "fixed scratch holds 8388608" in str(info.value)
     # a query that still needs the prologue is refused
     with pytest.raises(hb.UnsupportedPattern):
