@@ -669,42 +669,46 @@ hc_status simt_prefill(hc_context* ctx, const AttnShape& shape, const CacheView&
 }
 
 DecodePlan plan_decode(const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq, int target_items,
-                       bool allow_whole, int max_log_run) {
+                       bool allow_whole, int max_run_segments) {
     DecodePlan plan{};
-    int most_tiles = 0;
-    for (int b = 0; b < n_seq; ++b) most_tiles = std::max(most_tiles, row_tiles(map, meta.pos[b], meta.pos[b], shape.window).count);
+    int most_tiles = 0, segments = 0, most_segments = 1;
+    for (int b = 0; b < n_seq; ++b) {
+        most_tiles = std::max(most_tiles, row_tiles(map, meta.pos[b], meta.pos[b], shape.window).count);
+        const int n = visible_groups(meta.pos[b], meta.pos[b], shape.window, map.log_segment);
+        segments += n;
+        most_segments = std::max(most_segments, n);
+    }
     plan.tiles = std::max(most_tiles, 1);
-    // The coarsest cut that still gives the machine enough items: whole rows, then segments, then
-    // shorter and shorter runs of tiles.  Rows of a tile or two are never cut: the merge would cost
-    // more than it saves.
+    plan.log_run = map.log_segment;
+    plan.run_segments = 1;
+    // The coarsest cut that still gives the machine enough items: whole rows, then runs of segments,
+    // then shorter and shorter runs of tiles.  Rows of a tile or two are never cut: the merge would
+    // cost more than it saves.
     if (allow_whole && (most_tiles <= 2 || n_seq * shape.kv_heads >= target_items)) {
         plan.finish = 1;
-        plan.log_run = map.log_segment;
         plan.slots = 1;
         return plan;
     }
-    int log_run = std::max(max_log_run, map.log_segment);
+    if (segments * shape.kv_heads >= target_items) {
+        plan.run_segments = std::max(1, std::min(max_run_segments, segments * shape.kv_heads / target_items));
+        plan.slots = most_segments;
+        return plan;
+    }
+    int log_run = map.log_segment - 1;
     for (; log_run > 0; --log_run) {
         int items = 0;
         for (int b = 0; b < n_seq; ++b) items += visible_groups(meta.pos[b], meta.pos[b], shape.window, log_run);
         if (items * shape.kv_heads >= target_items) break;
     }
     plan.log_run = log_run;
-    plan.tile_partials = log_run < map.log_segment ? 1 : 0;
-    if (plan.tile_partials) {
-        plan.slots = plan.tiles;
-    } else {
-        for (int b = 0; b < n_seq; ++b) {
-            plan.slots = std::max(plan.slots, visible_groups(meta.pos[b], meta.pos[b], shape.window, map.log_segment));
-        }
-    }
+    plan.tile_partials = 1;
+    plan.slots = plan.tiles;
     return plan;
 }
 
-
 DecodePlan simt_plan_decode(const hc_context* ctx, const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq) {
     // These kernels always leave partials and merge: a whole-row plan is run as whole segments.
-    DecodePlan plan = plan_decode(shape, map, meta, n_seq, 4 * ctx->sm_count, true, map.log_segment);
+    DecodePlan plan = plan_decode(shape, map, meta, n_seq, 4 * ctx->sm_count, true, 1);
     if (plan.finish) {
         plan.finish = 0;
         plan.tile_partials = 0;
@@ -757,8 +761,9 @@ static hc_status launch_merge_rows(hc_context* ctx, const AttnShape& shape, cons
 
 hc_status launch_merge_decode(hc_context* ctx, const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq,
                               const Workspace& ws, const DecodePlan& plan, const EpilogueArgs& ep, cudaStream_t stream) {
-    if (!plan.tile_partials && plan.slots <= 8) {
-        // Few segment partials a row: a warp per row does it without the staging below.
+    if (!plan.tile_partials && (plan.slots <= 8 || n_seq * shape.q_heads >= 1024)) {
+        // Few segment partials a row, or rows enough to fill the machine with one warp each: a warp per
+        // row does it without the staging below.
         MergeRows rows{};
         rows.decode = 1;
         rows.tokens = n_seq;

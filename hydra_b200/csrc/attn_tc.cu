@@ -1044,13 +1044,12 @@ DecodePlan tc_plan_decode(const hc_context* ctx, const AttnShape& shape, const R
     // 3 .. 12 on uniform and ragged batches); the head_dim 256 kernel does not look ahead across
     // items: about one per thread block.
     const int target = (shape.head_dim == 256 ? 1 : 6) * std::max(ctx->sm_count, 1);
-    // Runs may cover several segments (one partial each): up to 64 tiles.
-    DecodePlan plan = plan_decode(shape, map, meta, n_seq, target, true, 6);
+    DecodePlan plan = plan_decode(shape, map, meta, n_seq, target, true, 64);
     if (plan.finish && row_state_floats(ctx, shape) > part_o_floats) {
         // A whole row that spans two segments needs the second fold's state, for which there is no room.
         bool spans = false;
         for (int b = 0; b < n_seq; ++b) spans = spans || visible_groups(meta.pos[b], meta.pos[b], shape.window, map.log_segment) > 1;
-        if (spans) plan = plan_decode(shape, map, meta, n_seq, target, false, 6);
+        if (spans) plan = plan_decode(shape, map, meta, n_seq, target, false, 64);
     }
     return plan;
 }
@@ -1073,7 +1072,17 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
     // One item per (sequence, kv head, run of the sequence's visible key tiles).
     int next = 0;
     for (int b = 0; b < n_seq; ++b) {
-        const int n = plan.finish ? 1 : visible_groups(meta.pos[b], meta.pos[b], shape.window, plan.log_run);
+        int n = 1;
+        if (plan.tile_partials) {
+            n = visible_groups(meta.pos[b], meta.pos[b], shape.window, plan.log_run);
+        } else if (!plan.finish) {
+            // The sequence's segments in runs of one size, about plan.run_segments each.
+            const int segments = visible_groups(meta.pos[b], meta.pos[b], shape.window, cache.map.log_segment);
+            const int want = (segments + plan.run_segments - 1) / plan.run_segments;
+            const int run = (segments + want - 1) / want;
+            n = (segments + run - 1) / run;
+            args.seq_run[b] = static_cast<unsigned short>(run);
+        }
         args.item_start[b] = next;
         args.seq_slots[b] = static_cast<unsigned short>(n);
         args.seq_magic[b] = division_magic(uint32_t(n), uint32_t(n) * uint32_t(shape.kv_heads));

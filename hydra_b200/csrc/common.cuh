@@ -171,6 +171,16 @@ __host__ __device__ __forceinline__ TileRange group_tiles(const RowMap& map, int
     const int g0 = group << log_tiles, g1 = g0 + (1 << log_tiles) - 1;
     return owned_tiles(map, g0 > tile_lo ? g0 : tile_lo, g1 < tile_hi ? g1 : tile_hi);
 }
+// The tiles of `count` consecutive segments, the first one `first_ordinal` segments after the block's
+// first visible segment.
+__host__ __device__ __forceinline__ TileRange segment_run_tiles(const RowMap& map, int first_pos, int last_pos, int window,
+                                                               int first_ordinal, int count) {
+    const int tile_lo = first_visible_tile(first_pos, window);
+    const int tile_hi = last_pos / kTileKeys;
+    const int segment = (tile_lo >> map.log_segment) + first_ordinal;
+    const int g0 = segment << map.log_segment, g1 = ((segment + count) << map.log_segment) - 1;
+    return owned_tiles(map, g0 > tile_lo ? g0 : tile_lo, g1 < tile_hi ? g1 : tile_hi);
+}
 // All the key tiles of this rank that rows at positions first_pos..last_pos see.
 __host__ __device__ __forceinline__ TileRange row_tiles(const RowMap& map, int first_pos, int last_pos, int window) {
     return owned_tiles(map, first_visible_tile(first_pos, window), last_pos / kTileKeys);

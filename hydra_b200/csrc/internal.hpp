@@ -179,14 +179,15 @@ hc_status simt_decode(hc_context* ctx, const AttnShape& shape, const CacheView& 
 // How a decode launch cuts its rows' keys (see TcArgs in tc_common.cuh for the three ways).
 struct DecodePlan {
     int finish;          // whole rows per item, finished by the kernel itself
-    int log_run;         // otherwise: items are aligned runs of 2^log_run tiles
+    int log_run;         // tile partials: items are aligned runs of 2^log_run tiles
+    int run_segments;    // segment partials: about this many segments per item
     int tile_partials;   // the kernel writes one partial per tile (log_run < log_segment) rather than per segment
     int slots;           // partial slots per row
     int tiles;           // key tiles of the longest row (on this rank)
 };
-// The coarsest cut that gives at least target_items items, runs of 2^max_log_run tiles at most.
+// The coarsest cut that gives at least target_items items, runs of max_run_segments segments at most.
 DecodePlan plan_decode(const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq, int target_items,
-                       bool allow_whole, int max_log_run);
+                       bool allow_whole, int max_run_segments);
 // The cuts simt_decode and tc_decode make (the latter given the room for partials or row state).
 DecodePlan simt_plan_decode(const hc_context* ctx, const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq);
 DecodePlan tc_plan_decode(const hc_context* ctx, const AttnShape& shape, const RowMap& map, const BatchMeta& meta, int n_seq,

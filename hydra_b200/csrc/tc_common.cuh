@@ -29,12 +29,13 @@ struct TcArgs {
     //   finish != 0       an item is all the key tiles of one row tile and kv head (prefill) or of one
     //                     sequence and kv head (decode).  The kernel runs both folds and the epilogue,
     //                     keeping the second fold's values between segments in row_state.
-    //   otherwise         an item is an aligned run of 2^log_run tiles of those rows and the kernel writes
-    //                     partials to the workspace, `slots` per row at most: with tile_partials == 0
-    //                     (log_run >= map.log_segment: whole segments) each segment's partial, slot =
-    //                     ordinal of the segment; with tile_partials != 0 (decode only, log_run <
-    //                     map.log_segment) every tile's own partial, slot = ordinal of the tile among
-    //                     the row's tiles.  A merge kernel finishes the rows.
+    //   otherwise         the kernel writes partials to the workspace, `slots` per row at most, and a
+    //                     merge kernel finishes the rows.  With tile_partials == 0 an item is a run of
+    //                     whole segments (one in prefill; seq_run[b] in decode, so that a sequence's
+    //                     items are of one size) and leaves each segment's partial, slot = ordinal of
+    //                     the segment.  With tile_partials != 0 (decode only) an item is an aligned run
+    //                     of 2^log_run tiles, log_run < map.log_segment, and leaves every tile's own
+    //                     partial, slot = ordinal of the tile among the row's tiles.
     int decode;
     int slots;
     int finish;
@@ -48,6 +49,7 @@ struct TcArgs {
     // Decode: sequence b has seq_slots[b] runs; its items, kv head major, start at item_start[b].
     int item_start[kMaxBatch + 1];
     unsigned short seq_slots[kMaxBatch];
+    unsigned short seq_run[kMaxBatch];   // segments per run of sequence b (decode, segment partials)
     uint32_t seq_magic[kMaxBatch];       // division by seq_slots[b]
     BatchMeta meta;
 };
@@ -108,8 +110,15 @@ __device__ __forceinline__ TcItem decode_item(const TcArgs& args, int index) {
         w.seq = args.seq;
     }
     const int last_pos = w.first_pos + w.valid_tokens - 1;
-    const TileRange tiles = args.finish ? row_tiles(args.map, w.first_pos, last_pos, args.window)
-                                        : group_tiles(args.map, w.first_pos, last_pos, args.window, w.slot, args.log_run);
+    TileRange tiles;
+    if (args.finish) {
+        tiles = row_tiles(args.map, w.first_pos, last_pos, args.window);
+    } else if (args.decode && !args.tile_partials) {
+        const int run = args.seq_run[w.row0];           // the sequence's segments in runs of one size
+        tiles = segment_run_tiles(args.map, w.first_pos, last_pos, args.window, w.slot * run, run);
+    } else {
+        tiles = group_tiles(args.map, w.first_pos, last_pos, args.window, w.slot, args.log_run);
+    }
     w.tile_first = tiles.first;
     w.n_tiles = tiles.count;
     w.first_segment = first_visible_tile(w.first_pos, args.window) >> args.map.log_segment;
