@@ -1009,20 +1009,29 @@ hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_sto
     args.log_run = cache.map.log_segment;
     const int tokens_per_tile = kRows / shape.group;
     args.mtiles = (tokens + tokens_per_tile - 1) / tokens_per_tile;
-    // Segments a row tile spans, at most.
-    int slots = 1;
+    // Segments and key tiles a row tile spans, at most.
+    int slots = 1, most_tiles = 1;
     for (int mtile = 0; mtile < args.mtiles; ++mtile) {
         const int first = first_position + mtile * tokens_per_tile;
         const int last = first_position + std::min((mtile + 1) * tokens_per_tile, tokens) - 1;
         slots = std::max(slots, visible_groups(first, last, shape.window, cache.map.log_segment));
+        most_tiles = std::max(most_tiles, row_tiles(cache.map, first, last, shape.window).count);
     }
-    // Whole rows per item when that alone fills the machine or nothing could be split; otherwise one
-    // item per (row tile, kv head, segment), merged afterwards.
+    // Whole rows per item, or one item per (row tile, kv head, segment) merged afterwards: whichever
+    // the longest thread block finishes first, in units of one key tile's time.  An item costs its
+    // tiles plus a start and an end (about four tiles' worth; eight for head_dim 256, whose kernel
+    // does not look ahead across items), the merge and its launch about ten.  Measured on one
+    // GPT-OSS chunk of 512 tokens with 1, 2 and 4 kv heads: the model picks the faster of the two
+    // in all but ties.
     const int whole_items = args.mtiles * shape.kv_heads;
     const size_t rows = size_t(tokens) * shape.q_heads;
     const bool can_split = slots > 1 && rows * slots * shape.head_dim <= ws.part_o_floats && rows * slots * 2 <= ws.part_ml_floats;
     const bool can_finish = slots == 1 || row_state_floats(ctx, shape) <= ws.part_o_floats;
-    const bool whole = !can_split || (can_finish && 2 * whole_items > ctx->sm_count);
+    const int sms = std::max(ctx->sm_count, 1);
+    const int item_cost = shape.head_dim == 256 ? 8 : 4;
+    const int whole_time = ((whole_items + sms - 1) / sms) * (most_tiles + item_cost);
+    const int split_time = ((whole_items * slots + sms - 1) / sms) * (std::min(most_tiles, 1 << cache.map.log_segment) + item_cost) + 10;
+    const bool whole = !can_split || (can_finish && whole_time <= split_time);
     if (whole && !can_finish) {
         return fail(HC_KV_OVERFLOW, "prefill: the attention workspace is too small for this chunk (" + std::to_string(tokens) +
                                         " tokens over " + std::to_string(slots) + " segments)");
