@@ -162,7 +162,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     reg_dealloc<LT::kRegsControl>();
     if (warp == 0) {
         // ===== producer: one stream of tiles across all of this CTA's items =====
-        if (lane == 0) {
+        if (LT::kStages >= 4 && lane == 0) {
+            // K(t) then V(t), tile by tile.
             uint32_t t = 0;
             bool ok = true;
             for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk)) {
@@ -190,6 +191,50 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                         tma_load_3d(v_smem + slot * LT::kTileBytes + b * (kTileKeys * 128), &tmap_v,
                                     &bars->v_full[slot], b * 64, row0, plane);
                     }
+                }
+            }
+        }
+        // With the two stages of d = 128 that lockstep leaves the K ring idle: the S issuer takes a K tile
+        // up to three tiles before the O issuer takes the V tile of the same keys.  There the K tiles
+        // run ahead of the V tiles, each stream with its own walk over the items (measured: 61 -> 57 us
+        // on a 512-token chunk at context 4096; with the four stages of d = 64 it is slower, 72 -> 74 us
+        // and 77 -> 85 us in decode, where the second walk's item decoding sits in the producer's path).
+        if (LT::kStages < 4 && lane == 0) {
+            constexpr int kKeysAhead = 3;
+            struct Cursor {
+                TcItemIter walk;
+                int j;
+                uint32_t t;
+            };
+            Cursor ck, cv;
+            ck.walk = items_begin(args);
+            ck.j = 0;
+            ck.t = 0;
+            cv = ck;
+            bool ok = true;
+            while (ok && (ck.walk.item < args.n_items || cv.walk.item < args.n_items)) {
+                const bool keys = ck.walk.item < args.n_items && (ck.t < cv.t + kKeysAhead || cv.walk.item >= args.n_items);
+                Cursor& c = keys ? ck : cv;
+                const int slot = int(c.t % LT::kStages);
+                const uint32_t round = c.t / LT::kStages;
+                uint64_t* empty = keys ? &bars->k_empty[slot] : &bars->v_empty[slot];
+                if (round > 0 && !mbar_wait(empty, (round - 1) & 1, abort_flag, args.status, keys ? 1 : 2)) {
+                    ok = false;
+                    break;
+                }
+                const TcItem& w = c.walk.w;
+                const int plane = w.seq * args.kv_heads + w.kv_head;
+                const int row0 = row_of_tile(args.map, w.tile_first + c.j * world);
+                uint64_t* full = keys ? &bars->k_full[slot] : &bars->v_full[slot];
+                unsigned char* dst = (keys ? k_smem : v_smem) + slot * LT::kTileBytes;
+                mbar_expect_tx(full, LT::kTileBytes);
+                for (int b = 0; b < LT::kBlocks; ++b) {
+                    tma_load_3d(dst + b * (kTileKeys * 128), keys ? &tmap_k : &tmap_v, full, b * 64, row0, plane);
+                }
+                ++c.t;
+                if (++c.j == w.n_tiles) {
+                    c.j = 0;
+                    items_next(args, c.walk);
                 }
             }
         }
