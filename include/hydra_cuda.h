@@ -182,7 +182,14 @@ HC_API hc_status hc_inverse_frequencies(int head_dim, double theta, int rotating
  * Allocates, per layer, K and V as bf16 [max_seqs][kv_heads][capacity][head_dim] (head-major, so
  * one head's history is contiguous), zero-filled, plus the split-attention workspace.
  * `prefill_chunk` is KVCache.prefillChunk (512 in the reference): a ring holds
- * window + prefill_chunk rows, rounded up to a multiple of 128.  `shard` may be NULL. */
+ * window + prefill_chunk rows, rounded up to a multiple of 128.  `shard` may be NULL.
+ *
+ * The call also fixes how each layer groups its 128-key tiles into segments (1024 or 4096 keys),
+ * from the layer's head counts, prefill_chunk, max_seqs and the device's SM count: the attention
+ * kernels fold tiles into segment partials and segment partials into rows, and a launch may spread
+ * a row's segments over thread blocks.  All calls on one cache agree bit for bit (chunked prefill,
+ * one-shot prefill, token-by-token decode, any batch); two caches of different geometry may differ
+ * in the last bits. */
 HC_API hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n_layers,
                                     int context_length, int prefill_chunk, int max_seqs,
                                     const hc_shard_desc* shard, hc_kv_cache** out);
@@ -281,8 +288,10 @@ HC_API hc_status hc_attention_decode(hc_context* ctx, hc_kv_cache* cache, int la
  *
  *   - q must be bf16, already normalised and rotated: io_dtype HC_BF16, norm_q 0, rope NULL, gate
  *     none or HC_GATE_SEPARATE.  1 to 64 sequences; not for sequence-sharded caches.
- *   - A call whose partials (n_seq * q_heads * visible_tiles * (head_dim + 2) floats) exceed the
- *     limit is refused with HC_KV_OVERFLOW and a message that states both sizes.
+ *   - A call whose partials (n_seq * q_heads * slots * (head_dim + 2) floats, where slots is the
+ *     number of segments of 1024 or 4096 keys, or of 128-key tiles, that the library cuts the longest
+ *     sequence into for this batch) exceed the limit is refused with HC_KV_OVERFLOW and a message
+ *     that states both sizes.
  *   - It runs the same kernels as hc_attention_decode (tcgen05 for head_dim 64, 128, 256, CUDA
  *     cores otherwise, params->kernel_path honoured) with the partials redirected, so its output
  *     equals hc_attention_decode's bit for bit.
