@@ -377,6 +377,45 @@ def bench_c4(ctx, ranks, peaks, repeat):
     }
 
 
+def bench_projections(ctx, ranks, peaks, repeat):
+    """The Q, K, V and O projections of one C2 layer for the whole 4096-token prompt through hc_linear
+    (tcgen05 GEMM), the rows of §8(f) that bracket the attention path.  With N > 1 the weights are
+    split like the heads: Q/K/V by output rows, O by input columns (its partial sums would be reduced
+    by the next op)."""
+    import torch
+    import hydra_b200 as hb
+    from hydra_b200 import workloads as wl
+    full = wl.config("C2")
+    backend = hb.AttentionBackend(ctx)
+    hidden, tokens = 2880, full.prompt
+    q_out = full.q_heads * full.head_dim // ranks.world
+    kv_out = full.kv_heads * full.head_dim // ranks.world
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    bf = torch.bfloat16
+    x = torch.randn(tokens, hidden, device="cuda", generator=gen).to(bf)
+    attn = torch.randn(tokens, q_out, device="cuda", generator=gen).to(bf)
+    weights = [(torch.randn(n, hidden, device="cuda", generator=gen) * 0.02).to(bf) for n in (q_out, kv_out, kv_out)]
+    biases = [torch.randn(n, device="cuda", generator=gen).to(bf) for n in (q_out, kv_out, kv_out)]
+    outs = [torch.empty(tokens, n, device="cuda", dtype=bf) for n in (q_out, kv_out, kv_out)]
+    w_o = (torch.randn(hidden, q_out, device="cuda", generator=gen) * 0.02).to(bf)
+    b_o = torch.randn(hidden, device="cuda", generator=gen).to(bf)
+    y_o = torch.empty(tokens, hidden, device="cuda", dtype=torch.float32)
+    stream = torch.cuda.current_stream()
+
+    def step(_):
+        for w, b, y in zip(weights, biases, outs):
+            backend.linear(x, w, b, y, tokens, hidden, w.shape[0], y_dtype=hb.capi.HC_BF16, stream=stream)
+        backend.linear(attn, w_o, b_o, y_o, tokens, q_out, hidden, y_dtype=hb.capi.HC_F32, stream=stream)
+
+    ms = ranks.max(typical(Timer(stream, 256 << 20).run(step, repeat)))
+    flops = 2.0 * tokens * hidden * (q_out + 2 * kv_out) + 2.0 * tokens * q_out * hidden
+    tflops = flops * ranks.world / (ms * 1e-3) / 1e12
+    return {"workload": f"C2 layer projections for {tokens} tokens: hidden {hidden} -> q {q_out}, k {kv_out}, v {kv_out} "
+                        f"(bf16 out), attention {q_out} -> hidden (fp32 out), bias on all four; four hc_linear calls",
+            "ms": ms, "tflops": tflops, "frac_of_tensor_peak": tflops / (peaks["bf16_tflops"] * ranks.world),
+            "l2": "flushed before each timed pass"}
+
+
 def bench_c5(ctx, ranks, peaks, repeat):
     """C5: one batched decode step over 64 ragged sequences, the window-128 layer and the full layer."""
     import torch
@@ -585,6 +624,7 @@ def run_cuda(args):
             configs[name] = bench_prefill_config(name, ctx, ranks, peaks, repeat)
         configs["C4"] = bench_c4(ctx, ranks, peaks, 12)
         configs["C5"] = bench_c5(ctx, ranks, peaks, 8)
+        configs["projections"] = bench_projections(ctx, ranks, peaks, 8)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -626,6 +666,8 @@ def run_case(args):
     import torch
     import hydra_b200 as hb
     case = args.case
+    if case == "linear":
+        return run_linear_case(args)
     d = 256 if case.endswith("256") or case == "c4" else 64
     qh, kvh = (16, 2) if case == "c4" else ((16, 8) if d == 256 else (64, 8))
     ctx = hb.Context(0)
@@ -675,6 +717,31 @@ def run_case(args):
     return 0
 
 
+def run_linear_case(args):
+    """hc_linear on C2's q_proj for the whole prompt: 4096 tokens x 2880 -> 4096 (48 output tiles of
+    128 x 256 per 128 tokens; 96.6 GFLOP)."""
+    import torch
+    import hydra_b200 as hb
+    ctx = hb.Context(0)
+    backend = hb.AttentionBackend(ctx)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    tokens, n_in, n_out = 4096, 2880, 4096
+    x = torch.randn(tokens, n_in, device="cuda", generator=gen).to(torch.bfloat16)
+    w = (torch.randn(n_out, n_in, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+    b = torch.randn(n_out, device="cuda", generator=gen).to(torch.bfloat16)
+    y = torch.empty(tokens, n_out, device="cuda", dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream()
+    times = Timer(stream, 256 << 20).run(lambda _: backend.linear(x, w, b, y, tokens, n_in, n_out, y_dtype=hb.capi.HC_BF16,
+                                                                  stream=stream), args.repeat, warm=min(3, args.repeat - 1))
+    ctx.check()
+    best = min(times)
+    work = 2.0 * tokens * n_in * n_out
+    print(f"linear {tokens} x {n_in} -> {n_out}: {best * 1e3:.1f} us per call, {work / (best * 1e-3) / 1e12:.1f} TFLOP/s "
+          f"(median {statistics.median(times) * 1e3:.1f} us over {len(times)} calls)")
+    ctx.close()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -683,7 +750,7 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="only the headline configuration (C2)")
-    ap.add_argument("--case", default=None, choices=["prefill", "decode", "prefill256", "decode256", "c4"])
+    ap.add_argument("--case", default=None, choices=["prefill", "decode", "prefill256", "decode256", "c4", "linear"])
     ap.add_argument("--repeat", type=int, default=3)
     args = ap.parse_args()
     if args.case:

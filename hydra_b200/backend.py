@@ -461,6 +461,14 @@ class AttentionBackend:
                                                       _ptr(query), _ptr(output), tokens, first_position,
                                                       ctypes.byref(s), _stream(stream)))
 
+    # denseProjection (ForwardEncoder.swift:160, BatchEncoder.swift:104): y = x W^T (+ bias) on the tensor cores
+    def linear(self, x, weight, bias, y, tokens: int, in_features: int, out_features: int,
+               y_dtype: int = capi.HC_F32, stream=None) -> None:
+        """x bf16 [tokens][in_features], weight bf16 [out_features][in_features] (the reference's
+        row-major layout), bias bf16 [out_features] or None, y fp32 or bf16 [tokens][out_features]."""
+        _check(self._lib.hc_linear(self.ctx.handle, _ptr(x), _ptr(weight), _ptr(bias) if bias is not None else None,
+                                   _ptr(y), tokens, in_features, out_features, y_dtype, _stream(stream)))
+
     # rmsNormHeads (ForwardEncoder.swift:535) / rmsNormHeadsBatch (BatchEncoder.swift:429)
     def rms_norm_heads(self, vector, scale, tokens: int, heads: int, head_dim: int, eps: float,
                        io_dtype: int = capi.HC_F32, stream=None) -> None:

@@ -973,6 +973,21 @@ hc_status hc_attention_combine(hc_context* ctx, const void* gathered, int world,
                           params->head_dim, ep, static_cast<cudaStream_t>(stream));
 }
 
+hc_status hc_linear(hc_context* ctx, const void* x, const void* w, const void* bias, void* y, int tokens,
+                    int in_features, int out_features, int y_dtype, void* stream) {
+    if (!ctx || !x || !w || !y) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    if (tokens < 0 || in_features <= 0 || out_features <= 0) return fail(HC_INVALID_ARGUMENT, "bad sizes");
+    if (y_dtype != HC_F32 && y_dtype != HC_BF16) return fail(HC_INVALID_ARGUMENT, "y_dtype must be HC_F32 or HC_BF16");
+    if (in_features % 64 != 0) {
+        return fail(HC_DIM_MISMATCH, "hc_linear: in_features " + std::to_string(in_features) + " must be a multiple of 64");
+    }
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15) {
+        return fail(HC_INVALID_ARGUMENT, "hc_linear: x, w and y must be 16-byte aligned");
+    }
+    if (tokens == 0) return HC_OK;
+    return linear_tc(ctx, x, w, bias, y, tokens, in_features, out_features, y_dtype, static_cast<cudaStream_t>(stream));
+}
+
 hc_status hc_rms_norm_heads(hc_context* ctx, void* vector, const void* weight_bf16, int tokens, int heads,
                             int head_dim, float eps, int io_dtype, void* stream) {
     if (!ctx || !vector || tokens < 0 || heads <= 0) return fail(HC_INVALID_ARGUMENT, "bad arguments");

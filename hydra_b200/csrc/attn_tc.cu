@@ -949,6 +949,20 @@ bool dim_ok(int d) { return d == 64 || d == 128 || d == 256; }
 
 }  // namespace
 
+hc_status tc_encode_2d(void* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn encode = encode_tiled();
+    if (!encode) return fail(HC_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(cols) * 2};
+    const cuuint32_t box[2] = {64, cuuint32_t(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(static_cast<CUtensorMap*>(map), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                               strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(HC_CUDA_ERROR, "cuTensorMapEncodeTiled failed with code " + std::to_string(int(rc)));
+    return HC_OK;
+}
+
 bool tc_supported(const AttnShape& shape) { return dim_ok(shape.head_dim) && shape.group <= 16; }
 
 hc_status tc_make_tensor_maps(hc_kv_cache* cache, hc_layer_store& layer) {

@@ -206,6 +206,9 @@ hc_status launch_combine(hc_context* ctx, const float* gathered, int world, int 
 hc_status static_scratch_prepare(int device, float** address);
 
 // attn_tc.cu
+// A tensor map (CUtensorMap behind `map`) over a row-major bf16 matrix: boxes of 64 columns x box_rows
+// rows, 128-byte swizzle, zeros beyond the edges.
+hc_status tc_encode_2d(void* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
 bool tc_supported(const AttnShape& shape);
 hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer,
                      const CacheView& cache, int seq, const uint16_t* q, int tokens,
@@ -213,6 +216,9 @@ hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_sto
 hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer,
                     const CacheView& cache, const BatchMeta& meta, int n_seq, const uint16_t* q,
                     const Workspace& ws, const EpilogueArgs& ep, cudaStream_t stream);
+// linear_tc.cu
+hc_status linear_tc(hc_context* ctx, const void* x, const void* w, const void* bias, void* y, int tokens,
+                    int in_features, int out_features, int y_dtype, cudaStream_t stream);
 // attn_tc256.cu (args_ptr: the TcArgs of tc_common.cuh)
 hc_status launch_tc256(hc_context* ctx, const void* tmap_k, const void* tmap_v, const void* args_ptr,
                        int n_items, cudaStream_t stream);

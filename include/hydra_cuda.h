@@ -176,6 +176,23 @@ HC_API hc_status hc_yarn_inverse_frequencies(int head_dim, double base, int init
 HC_API hc_status hc_inverse_frequencies(int head_dim, double theta, int rotating_pairs,
                                         double* inv_freq);
 
+/* ---- Projections -------------------------------------------------------------------------- */
+
+/* y[t][o] = sum_i x[t][i] * w[o][i] (+ bias[o]): the Q, K, V and O projections on either side of
+ * the attention calls, on the tensor cores (tcgen05, fp32 accumulate).  Replaces
+ * ForwardEncoder.denseProjection (Sources/HydraMetal/ForwardEncoder.swift:160-190) and
+ * BatchEncoder.denseProjection (Sources/HydraMetal/BatchEncoder.swift:104), i.e. bf16_gemv and its
+ * batched and tiled forms (Sources/HydraMetal/Shaders/dense.metal:14-60, batch.metal:36-88,
+ * tiled.metal:48-120); the weight keeps the reference's layout.
+ *   x     bf16 [tokens][in_features]      (the reference passes fp32 activations; round them to bf16)
+ *   w     bf16 [out_features][in_features], row-major
+ *   bias  bf16 [out_features] or NULL
+ *   y     fp32 or bf16 [tokens][out_features], per y_dtype
+ * in_features must be a multiple of 64; x, w and y 16-byte aligned.  For Qwen's 2x-tall q_proj pass
+ * the whole weight: y is then the interleaved query/gate buffer that HC_GATE_INTERLEAVED reads. */
+HC_API hc_status hc_linear(hc_context* ctx, const void* x, const void* w, const void* bias, void* y,
+                           int tokens, int in_features, int out_features, int y_dtype, void* stream);
+
 /* ---- KV cache ------------------------------------------------------------------------------- */
 
 /* Replaces KVCache.init(model:contextLength:device:) (Sources/HydraMetal/KVCache.swift:132-182).

@@ -158,6 +158,16 @@ def apply_rope_position(x, position, inv_freq) -> np.ndarray:
     return out
 
 
+def linear(x, weight, bias=None) -> np.ndarray:
+    """y[t][o] = sum_i weight[o][i] * x[t][i] + bias[o] in double: ReferenceLayer.matVec
+    (Sources/HydraReference/ReferenceLayer.swift:104-113) and the Gemma / Qwen layers' `project`
+    (Sources/HydraReference/QwenReferenceLayer.swift:116-118), one token per row of x."""
+    y = _f64(x) @ _f64(weight).T
+    if bias is not None:
+        y = y + _f64(bias)
+    return y
+
+
 def sdpa(q, k, v, sinks, sm_scale, window=0) -> np.ndarray:
     """ReferenceOps.sdpa.  q [T][kv][mult][d]; k, v [T][kv][d]; sinks [kv*mult] -> [T][kv*mult*d]."""
     q, k, v, sinks = _f64(q), _f64(k), _f64(v), _f64(sinks)
