@@ -463,11 +463,19 @@ class AttentionBackend:
 
     # denseProjection (ForwardEncoder.swift:160, BatchEncoder.swift:104): y = x W^T (+ bias) on the tensor cores
     def linear(self, x, weight, bias, y, tokens: int, in_features: int, out_features: int,
-               y_dtype: int = capi.HC_F32, stream=None) -> None:
+               y_dtype: int = capi.HC_F32, residual=None, stream=None) -> None:
         """x bf16 [tokens][in_features], weight bf16 [out_features][in_features] (the reference's
-        row-major layout), bias bf16 [out_features] or None, y fp32 or bf16 [tokens][out_features]."""
+        row-major layout), bias bf16 [out_features] or None, residual fp32 like y or None (it may be
+        y itself), y fp32 or bf16 [tokens][out_features]."""
         _check(self._lib.hc_linear(self.ctx.handle, _ptr(x), _ptr(weight), _ptr(bias) if bias is not None else None,
-                                   _ptr(y), tokens, in_features, out_features, y_dtype, _stream(stream)))
+                                   _ptr(residual) if residual is not None else None, _ptr(y), tokens, in_features,
+                                   out_features, y_dtype, _stream(stream)))
+
+    # rmsNorm (ForwardEncoder.swift:141): the layer's input norm over whole rows
+    def rms_norm(self, x, scale, y, tokens: int, width: int, eps: float, x_dtype: int = capi.HC_F32,
+                 y_dtype: int = capi.HC_BF16, stream=None) -> None:
+        _check(self._lib.hc_rms_norm(self.ctx.handle, _ptr(x), _ptr(scale) if scale is not None else None, _ptr(y),
+                                     tokens, width, eps, x_dtype, y_dtype, _stream(stream)))
 
     # rmsNormHeads (ForwardEncoder.swift:535) / rmsNormHeadsBatch (BatchEncoder.swift:429)
     def rms_norm_heads(self, vector, scale, tokens: int, heads: int, head_dim: int, eps: float,

@@ -973,8 +973,19 @@ hc_status hc_attention_combine(hc_context* ctx, const void* gathered, int world,
                           params->head_dim, ep, static_cast<cudaStream_t>(stream));
 }
 
-hc_status hc_linear(hc_context* ctx, const void* x, const void* w, const void* bias, void* y, int tokens,
-                    int in_features, int out_features, int y_dtype, void* stream) {
+hc_status hc_rms_norm(hc_context* ctx, const void* x, const void* scale_bf16, void* y, int tokens, int width, float eps,
+                      int x_dtype, int y_dtype, void* stream) {
+    if (!ctx || !x || !y) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    if (tokens < 0 || width <= 0) return fail(HC_INVALID_ARGUMENT, "bad sizes");
+    if ((x_dtype != HC_F32 && x_dtype != HC_BF16) || (y_dtype != HC_F32 && y_dtype != HC_BF16)) {
+        return fail(HC_INVALID_ARGUMENT, "dtypes must be HC_F32 or HC_BF16");
+    }
+    return launch_rms_norm_rows(ctx, x, static_cast<const uint16_t*>(scale_bf16), y, tokens, width, eps, x_dtype, y_dtype,
+                                static_cast<cudaStream_t>(stream));
+}
+
+hc_status hc_linear(hc_context* ctx, const void* x, const void* w, const void* bias, const void* residual, void* y,
+                    int tokens, int in_features, int out_features, int y_dtype, void* stream) {
     if (!ctx || !x || !w || !y) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
     if (tokens < 0 || in_features <= 0 || out_features <= 0) return fail(HC_INVALID_ARGUMENT, "bad sizes");
     if (y_dtype != HC_F32 && y_dtype != HC_BF16) return fail(HC_INVALID_ARGUMENT, "y_dtype must be HC_F32 or HC_BF16");
@@ -984,8 +995,10 @@ hc_status hc_linear(hc_context* ctx, const void* x, const void* w, const void* b
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15) {
         return fail(HC_INVALID_ARGUMENT, "hc_linear: x, w and y must be 16-byte aligned");
     }
+    if (residual && y_dtype != HC_F32) return fail(HC_INVALID_ARGUMENT, "hc_linear: a residual needs an fp32 y");
     if (tokens == 0) return HC_OK;
-    return linear_tc(ctx, x, w, bias, y, tokens, in_features, out_features, y_dtype, static_cast<cudaStream_t>(stream));
+    return linear_tc(ctx, x, w, bias, static_cast<const float*>(residual), y, tokens, in_features, out_features, y_dtype,
+                     static_cast<cudaStream_t>(stream));
 }
 
 hc_status hc_rms_norm_heads(hc_context* ctx, void* vector, const void* weight_bf16, int tokens, int heads,

@@ -164,6 +164,8 @@ hc_status check_cuda(cudaError_t err, const char* what);
 
 // prologue.cu
 hc_status launch_prepare(hc_context* ctx, const PrepArgs& args, cudaStream_t stream);
+hc_status launch_rms_norm_rows(hc_context* ctx, const void* x, const uint16_t* scale, void* out, int tokens, int width,
+                               float eps, int x_dtype, int out_dtype, cudaStream_t stream);
 hc_status launch_split_query_gate(hc_context* ctx, const void* combined, void* query, void* gate,
                                   int tokens, int heads, int d, int dtype, cudaStream_t stream);
 hc_status launch_output_gate(hc_context* ctx, void* output, const void* gate, size_t count,
@@ -217,8 +219,8 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
                     const CacheView& cache, const BatchMeta& meta, int n_seq, const uint16_t* q,
                     const Workspace& ws, const EpilogueArgs& ep, cudaStream_t stream);
 // linear_tc.cu
-hc_status linear_tc(hc_context* ctx, const void* x, const void* w, const void* bias, void* y, int tokens,
-                    int in_features, int out_features, int y_dtype, cudaStream_t stream);
+hc_status linear_tc(hc_context* ctx, const void* x, const void* w, const void* bias, const float* residual, void* y,
+                    int tokens, int in_features, int out_features, int y_dtype, cudaStream_t stream);
 // attn_tc256.cu (args_ptr: the TcArgs of tc_common.cuh)
 hc_status launch_tc256(hc_context* ctx, const void* tmap_k, const void* tmap_v, const void* args_ptr,
                        int n_items, cudaStream_t stream);

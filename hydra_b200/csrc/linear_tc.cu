@@ -15,7 +15,7 @@
 //   warp 0      TMA producer: x tile (128 x 64) and w tile (256 x 64) per K step into a 4-stage ring
 //   warp 1      MMA issuer: four tcgen05.mma (M 128, N 256, K 16) per K step into one of two
 //               accumulators in tensor memory (2 x 256 columns)
-//   warps 4-7   epilogue: the finished accumulator from tensor memory, + bias, to y (fp32 or bf16),
+//   warps 4-7   epilogue: the finished accumulator from tensor memory, + bias (+ residual), to y (fp32 or bf16),
 //               thread = row, while the next tile's MMAs fill the other accumulator
 // Every mbarrier wait is bounded and reports through the context's status word.
 
@@ -44,6 +44,7 @@ struct LinBarriers {
 
 struct LinArgs {
     const uint16_t* bias;     // bf16 [out_features] or null
+    const float* residual;    // fp32 [tokens][out_features] added to the result, or null (may be y itself)
     void* y;                  // [tokens][out_features]
     int y_dtype;              // HC_F32 or HC_BF16
     int tokens, out_features;
@@ -170,6 +171,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                     r[i] = __fadd_rn(__uint_as_float(v[i]), b);
                 }
                 const size_t offset = size_t(row) * args.out_features + col0;
+                if (args.residual != nullptr) {
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (col0 + i < args.out_features) r[i] = __fadd_rn(r[i], __ldg(args.residual + offset + i));
+                    }
+                }
                 const bool whole = col0 + 32 <= args.out_features && (args.out_features & 7) == 0;
                 if (args.y_dtype == HC_F32) {
                     float* dst = reinterpret_cast<float*>(args.y) + offset;
@@ -215,14 +222,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 
 }  // namespace
 
-hc_status linear_tc(hc_context* ctx, const void* x, const void* w, const void* bias, void* y, int tokens,
-                    int in_features, int out_features, int y_dtype, cudaStream_t stream) {
+hc_status linear_tc(hc_context* ctx, const void* x, const void* w, const void* bias, const float* residual, void* y,
+                    int tokens, int in_features, int out_features, int y_dtype, cudaStream_t stream) {
     CUtensorMap tmap_x, tmap_w;
     hc_status st = tc_encode_2d(&tmap_x, x, uint64_t(tokens), uint64_t(in_features), kLinM);
     if (st == HC_OK) st = tc_encode_2d(&tmap_w, w, uint64_t(out_features), uint64_t(in_features), kLinN);
     if (st != HC_OK) return st;
     LinArgs args{};
     args.bias = static_cast<const uint16_t*>(bias);
+    args.residual = residual;
     args.y = y;
     args.y_dtype = y_dtype;
     args.tokens = tokens;

@@ -245,6 +245,38 @@ prepare_heads_kernel(const PrepArgs args) {
     }
 }
 
+// RMSNorm of whole rows (the layer's input norm): out = x * rsqrt(mean(x^2) + eps) * scale.  One block
+// per token; replaces rms_norm and rms_norm_batch (Sources/HydraMetal/Shaders/attention.metal:9-43,
+// batch.metal:184-218).  The output may be bf16, ready to be the A operand of hc_linear.
+__global__ void __launch_bounds__(256)
+rms_norm_rows_kernel(const void* __restrict__ x, const uint16_t* __restrict__ scale, void* __restrict__ out, int width,
+                     float eps, int x_dtype, int out_dtype) {
+    __shared__ float warp_sum[8];
+    __shared__ float inverse;
+    const size_t base = size_t(blockIdx.x) * width;
+    float partial = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = load_io(x, base + i, x_dtype);
+        partial = __fmaf_rn(v, v, partial);
+    }
+    #pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, offset);
+    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = partial;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int w = 0; w < int(blockDim.x >> 5); ++w) total += warp_sum[w];
+        inverse = rsqrtf(total / float(width) + eps);
+    }
+    __syncthreads();
+    const float inv = inverse;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = load_io(x, base + i, x_dtype);
+        const float w = scale != nullptr ? bf16_bits_to_float(scale[i]) : 1.0f;
+        store_io(out, base + i, out_dtype, __fmul_rn(__fmul_rn(v, inv), w));
+    }
+}
+
 __global__ void split_query_gate_kernel(const void* combined, void* query, void* gate, size_t count,
                                         int d, int dtype) {
     // count = tokens * heads * d; element e = (token*heads + head) * d + i
@@ -297,6 +329,14 @@ hc_status launch_prepare(hc_context* ctx, const PrepArgs& args, cudaStream_t str
     }
     ctx->launches += 1;
     return check_cuda(cudaGetLastError(), "prepare_heads_kernel launch");
+}
+
+hc_status launch_rms_norm_rows(hc_context* ctx, const void* x, const uint16_t* scale, void* out, int tokens, int width,
+                               float eps, int x_dtype, int out_dtype, cudaStream_t stream) {
+    if (tokens <= 0) return HC_OK;
+    rms_norm_rows_kernel<<<unsigned(tokens), 256, 0, stream>>>(x, scale, out, width, eps, x_dtype, out_dtype);
+    ctx->launches += 1;
+    return check_cuda(cudaGetLastError(), "rms_norm_rows_kernel launch");
 }
 
 hc_status launch_split_query_gate(hc_context* ctx, const void* combined, void* query, void* gate,

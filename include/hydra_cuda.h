@@ -186,12 +186,22 @@ HC_API hc_status hc_inverse_frequencies(int head_dim, double theta, int rotating
  * tiled.metal:48-120); the weight keeps the reference's layout.
  *   x     bf16 [tokens][in_features]      (the reference passes fp32 activations; round them to bf16)
  *   w     bf16 [out_features][in_features], row-major
- *   bias  bf16 [out_features] or NULL
- *   y     fp32 or bf16 [tokens][out_features], per y_dtype
+ *   bias      bf16 [out_features] or NULL
+ *   residual  fp32 [tokens][out_features] added to the result, or NULL; it may be y itself, which
+ *             is the layer's `hidden += o_proj(attention)` (Sources/HydraReference/ReferenceLayer.swift:186-187)
+ *   y         fp32 or bf16 [tokens][out_features], per y_dtype (fp32 with a residual)
  * in_features must be a multiple of 64; x, w and y 16-byte aligned.  For Qwen's 2x-tall q_proj pass
  * the whole weight: y is then the interleaved query/gate buffer that HC_GATE_INTERLEAVED reads. */
-HC_API hc_status hc_linear(hc_context* ctx, const void* x, const void* w, const void* bias, void* y,
-                           int tokens, int in_features, int out_features, int y_dtype, void* stream);
+HC_API hc_status hc_linear(hc_context* ctx, const void* x, const void* w, const void* bias,
+                           const void* residual, void* y, int tokens, int in_features,
+                           int out_features, int y_dtype, void* stream);
+
+/* y = x * rsqrt(mean(x^2) + eps) * scale over whole rows: the layer's input norm.  Replaces
+ * ForwardEncoder.rmsNorm (Sources/HydraMetal/ForwardEncoder.swift:141-157) and the batched kernel
+ * (Sources/HydraMetal/Shaders/batch.metal:184-218).  x fp32 or bf16 [tokens][width], scale bf16
+ * [width] or NULL (rmsNormUnscaled), y fp32 or bf16: bf16 is what hc_linear takes. */
+HC_API hc_status hc_rms_norm(hc_context* ctx, const void* x, const void* scale_bf16, void* y,
+                             int tokens, int width, float eps, int x_dtype, int y_dtype, void* stream);
 
 /* ---- KV cache ------------------------------------------------------------------------------- */
 
