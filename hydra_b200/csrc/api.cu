@@ -187,10 +187,19 @@ bool use_tensor_path(const hc_attn_params* p, const AttnShape& shape, hc_status*
 // The body shared by hc_attention_prefill and hc_attention_prefill_partial.
 // With k_fused / v_fused set (hc_layer_step; one pass, tokens <= the prologue workspace) the K/V
 // append of the same tokens rides in the Q prologue's launch.
+// When `ahead` is given (hc_prefill_chunks), the prologue launch goes to ahead->stream into the
+// ahead->slot-th prepared-query buffer, and `stream` waits for ahead->done, recorded behind it: the
+// prologue of a chunk can then run while the previous chunk's attention is still finishing.
+struct PrologueAhead {
+    cudaStream_t stream;
+    cudaEvent_t done;
+    int slot;
+};
+
 hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, const void* q,
                        void* out, int tokens, int first_position, const hc_attn_params* p,
                        bool partial_mode, cudaStream_t stream, const void* k_fused = nullptr,
-                       const void* v_fused = nullptr) {
+                       const void* v_fused = nullptr, const PrologueAhead* ahead = nullptr) {
     if (!ctx || !q || !out) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
     hc_status st = validate_params(cache, layer, p);
     if (st != HC_OK) return st;
@@ -219,7 +228,8 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
             PrepArgs args{};
             fill_common(args, p);
             int jobs = 0;
-            if (prep) fill_q_job(args.job[jobs++], p, q_rows, cache->ws.qprep);
+            uint16_t* prepared = cache->ws.qprep + (ahead ? size_t(ahead->slot) * cache->ws.qprep_slot_elems : 0);
+            if (prep) fill_q_job(args.job[jobs++], p, q_rows, prepared);
             if (k_fused) {
                 fill_kv_jobs(args, jobs, p, k_fused, v_fused);
                 jobs += 2;
@@ -230,9 +240,14 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
             args.batched = 0;
             args.seq = seq;
             args.cache = view;
-            st = launch_prepare(ctx, args, stream);
+            st = launch_prepare(ctx, args, ahead ? ahead->stream : stream);
             if (st != HC_OK) return st;
-            if (prep) q_bf16 = cache->ws.qprep;
+            if (ahead) {
+                cudaError_t err = cudaEventRecord(ahead->done, ahead->stream);
+                if (err == cudaSuccess) err = cudaStreamWaitEvent(stream, ahead->done, 0);
+                if (err != cudaSuccess) return check_cuda(err, "prefill: prologue event");
+            }
+            if (prep) q_bf16 = prepared;
         }
         EpilogueArgs ep{};
         ep.io_dtype = p->io_dtype;
@@ -652,7 +667,8 @@ hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n
         ws.qprep_tokens = std::max(std::max(prefill_chunk, std::min(max_seqs, kMaxBatch)), 1);
         ws.part_o_floats = part_o_floats;
         ws.part_ml_floats = part_ml_floats;
-        err = cudaMalloc(&ws.qprep, size_t(ws.qprep_tokens) * max_q_elems * 2);
+        ws.qprep_slot_elems = size_t(ws.qprep_tokens) * max_q_elems;
+        err = cudaMalloc(&ws.qprep, 2 * ws.qprep_slot_elems * 2);
         if (err == cudaSuccess) err = cudaMalloc(&ws.part_o, part_o_floats * sizeof(float));
         if (err == cudaSuccess) err = cudaMalloc(&ws.part_ml, part_ml_floats * sizeof(float));
         // Staging for the host-buffer entry points, two slots: q (twice as wide when the gate is
@@ -1105,19 +1121,47 @@ hc_status hc_prefill_chunks(hc_context* ctx, hc_kv_cache* cache, int layer, int 
     if (tokens <= 0 || chunk <= 0) return fail(HC_INVALID_ARGUMENT, "tokens and chunk must be positive");
     const int d = params->head_dim;
     const int mult = params->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
-    for (int start = 0; start < tokens; start += chunk) {
+    // On a linear (non-ring) layer a chunk's prologue (K/V append, query norm and rotation) touches
+    // nothing the previous chunk's attention reads, apart from the prepared-query buffer, which has
+    // two slots: it runs on a stream of its own, one chunk ahead, in the SMs the attention kernel
+    // leaves idle while its last thread blocks finish.  (On a ring the appended rows overwrite keys
+    // the previous chunk still attends to.)
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const hc_layer_store& L = cache->layers[size_t(layer)];
+    const bool ahead_ok = L.ring == 0 && chunk > 1 && chunk <= cache->ws.qprep_tokens && tokens > chunk && cache->copy_in != nullptr;
+    if (ahead_ok) {
+        cudaError_t err = cudaEventRecord(cache->entry, s);
+        if (err == cudaSuccess) err = cudaStreamWaitEvent(cache->copy_in, cache->entry, 0);
+        if (err != cudaSuccess) return check_cuda(err, "prefill chunks: entry event");
+    }
+    int index = 0;
+    for (int start = 0; start < tokens; start += chunk, ++index) {
         const int count = std::min(chunk, tokens - start);
         hc_attn_params local = *params;
         if (params->gate_layout == HC_GATE_SEPARATE) {
             local.gate = offset_rows(params->gate, size_t(start), size_t(params->q_heads) * d, params->io_dtype);
         }
-        st = hc_layer_step(ctx, cache, layer, seq,
-                           offset_rows(q, size_t(start), size_t(params->q_heads) * d * mult, params->io_dtype),
-                           offset_rows(k, size_t(start), size_t(params->kv_heads) * d, params->io_dtype),
-                           offset_rows(v, size_t(start), size_t(params->kv_heads) * d, params->io_dtype),
-                           const_cast<unsigned char*>(offset_rows(out, size_t(start), size_t(params->q_heads) * d, params->io_dtype)),
-                           count, first_position + start, &local, stream);
-        if (st != HC_OK) return st;
+        const void* q_rows = offset_rows(q, size_t(start), size_t(params->q_heads) * d * mult, params->io_dtype);
+        const void* k_rows = offset_rows(k, size_t(start), size_t(params->kv_heads) * d, params->io_dtype);
+        const void* v_rows = offset_rows(v, size_t(start), size_t(params->kv_heads) * d, params->io_dtype);
+        void* out_rows = const_cast<unsigned char*>(offset_rows(out, size_t(start), size_t(params->q_heads) * d, params->io_dtype));
+        if (ahead_ok && count > 1) {
+            const int slot = index & 1;
+            // The slot's prepared queries were last read by the attention of chunk index - 2.
+            if (index >= 2) {
+                const cudaError_t err = cudaStreamWaitEvent(cache->copy_in, cache->step_done[slot], 0);
+                if (err != cudaSuccess) return check_cuda(err, "prefill chunks: slot event");
+            }
+            const PrologueAhead ahead{cache->copy_in, cache->in_done[slot], slot};
+            st = prefill_impl(ctx, cache, layer, seq, q_rows, out_rows, count, first_position + start, &local, false, s,
+                              k_rows, v_rows, &ahead);
+            if (st != HC_OK) return st;
+            const cudaError_t err = cudaEventRecord(cache->step_done[slot], s);
+            if (err != cudaSuccess) return check_cuda(err, "prefill chunks: step event");
+        } else {
+            st = hc_layer_step(ctx, cache, layer, seq, q_rows, k_rows, v_rows, out_rows, count, first_position + start, &local, stream);
+            if (st != HC_OK) return st;
+        }
     }
     return HC_OK;
 }

@@ -96,7 +96,9 @@ struct EpilogueArgs {
 };
 
 struct Workspace {
-    uint16_t* qprep = nullptr;   // bf16 [qprep_tokens][q_heads][d]
+    uint16_t* qprep = nullptr;   // bf16 [2][qprep_tokens][q_heads][d]: two slots, so that a chunk's prologue can
+                                 // run while the previous chunk's attention still reads its queries
+    size_t qprep_slot_elems = 0; // elements of one slot
     int qprep_tokens = 0;
     float* part_o = nullptr;     // fp32 [rows][slots][d]: segment partials, rows and slots those of the call
     float* part_ml = nullptr;    // fp32 [rows][slots][2]
