@@ -264,7 +264,15 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
             ep.gate = q_rows;
         }
         if (tensor) {
-            st = tc_prefill(ctx, shape, L, view, seq, q_bf16, count, first_position + start, cache->ws, ep, stream);
+            // A chunk attended to on the second stream works in the upper halves of the workspace.
+            Workspace ws = cache->ws;
+            if (ahead) {
+                ws.part_o += size_t(ahead->slot) * ws.prefill_o_floats;
+                ws.part_ml += size_t(ahead->slot) * ws.prefill_ml_floats;
+                ws.part_o_floats = ws.prefill_o_floats;
+                ws.part_ml_floats = ws.prefill_ml_floats;
+            }
+            st = tc_prefill(ctx, shape, L, view, seq, q_bf16, count, first_position + start, ws, ep, stream);
         } else {
             st = simt_prefill(ctx, shape, view, seq, q_bf16, count, first_position + start, ep, stream);
         }
@@ -583,7 +591,7 @@ hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n
     cache->lengths.assign(size_t(max_seqs), 0);
     cache->layers.resize(size_t(n_layers));
 
-    size_t max_q_elems = 0, max_kv_elems = 0, part_o_floats = 0, part_ml_floats = 0;
+    size_t max_q_elems = 0, max_kv_elems = 0, part_o_floats = 0, part_ml_floats = 0, prefill_o_floats = 0, prefill_ml_floats = 0;
     hc_status st = HC_OK;
     for (int i = 0; i < n_layers && st == HC_OK; ++i) {
         hc_layer_store& L = cache->layers[size_t(i)];
@@ -653,20 +661,26 @@ hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n
         if (few_rows) {
             const size_t prefill_slots = size_t((((reach + kTileKeys - 1) / kTileKeys) >> kLogSegmentSmall) + 2);
             const size_t prefill_rows = size_t(prefill_chunk) * L.desc.q_heads;
-            part_o_floats = std::max(part_o_floats, prefill_rows * prefill_slots * d);
-            part_ml_floats = std::max(part_ml_floats, prefill_rows * prefill_slots * 2);
+            prefill_o_floats = std::max(prefill_o_floats, prefill_rows * prefill_slots * d);
+            prefill_ml_floats = std::max(prefill_ml_floats, prefill_rows * prefill_slots * 2);
         }
         // The tensor-core kernels keep a whole-row launch's second-fold state in the same buffer:
         // head_dim x 128 floats per thread block.
-        if (d == 64 || d == 128 || d == 256) part_o_floats = std::max(part_o_floats, size_t(std::max(ctx->sm_count, 1)) * d * 128);
+        if (d == 64 || d == 128 || d == 256) prefill_o_floats = std::max(prefill_o_floats, size_t(std::max(ctx->sm_count, 1)) * d * 128);
         st = tc_make_tensor_maps(cache, L);
     }
     if (st == HC_OK && max_q_elems == 0) st = fail(HC_UNSUPPORTED, "no layer keeps a key/value history");
     if (st == HC_OK) {
         hc::Workspace& ws = cache->ws;
         ws.qprep_tokens = std::max(std::max(prefill_chunk, std::min(max_seqs, kMaxBatch)), 1);
+        prefill_o_floats = (prefill_o_floats + 63) & ~size_t(63);
+        prefill_ml_floats = (prefill_ml_floats + 63) & ~size_t(63);
+        part_o_floats = std::max(part_o_floats, 2 * prefill_o_floats);
+        part_ml_floats = std::max(part_ml_floats, 2 * prefill_ml_floats);
         ws.part_o_floats = part_o_floats;
         ws.part_ml_floats = part_ml_floats;
+        ws.prefill_o_floats = prefill_o_floats;
+        ws.prefill_ml_floats = prefill_ml_floats;
         ws.qprep_slot_elems = size_t(ws.qprep_tokens) * max_q_elems;
         err = cudaMalloc(&ws.qprep, 2 * ws.qprep_slot_elems * 2);
         if (err == cudaSuccess) err = cudaMalloc(&ws.part_o, part_o_floats * sizeof(float));
@@ -1129,11 +1143,18 @@ hc_status hc_prefill_chunks(hc_context* ctx, hc_kv_cache* cache, int layer, int 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const hc_layer_store& L = cache->layers[size_t(layer)];
     const bool ahead_ok = L.ring == 0 && chunk > 1 && chunk <= cache->ws.qprep_tokens && tokens > chunk && cache->copy_in != nullptr;
+    // Nor does a chunk's attention read anything the previous chunk's attention writes (the workspace
+    // for segment partials and second-fold state exists twice): the chunks alternate between the
+    // caller's stream and a second one, and a chunk's thread blocks take over the SMs as the previous
+    // chunk's thread blocks leave them, instead of waiting for the last one.
+    const bool alternate = ahead_ok && cache->copy_out != nullptr;
     if (ahead_ok) {
         cudaError_t err = cudaEventRecord(cache->entry, s);
         if (err == cudaSuccess) err = cudaStreamWaitEvent(cache->copy_in, cache->entry, 0);
+        if (err == cudaSuccess && alternate) err = cudaStreamWaitEvent(cache->copy_out, cache->entry, 0);
         if (err != cudaSuccess) return check_cuda(err, "prefill chunks: entry event");
     }
+    bool other_used = false;
     int index = 0;
     for (int start = 0; start < tokens; start += chunk, ++index) {
         const int count = std::min(chunk, tokens - start);
@@ -1153,15 +1174,27 @@ hc_status hc_prefill_chunks(hc_context* ctx, hc_kv_cache* cache, int layer, int 
                 if (err != cudaSuccess) return check_cuda(err, "prefill chunks: slot event");
             }
             const PrologueAhead ahead{cache->copy_in, cache->in_done[slot], slot};
-            st = prefill_impl(ctx, cache, layer, seq, q_rows, out_rows, count, first_position + start, &local, false, s,
-                              k_rows, v_rows, &ahead);
+            const cudaStream_t attend_on = (alternate && slot == 1) ? cache->copy_out : s;
+            other_used = other_used || attend_on != s;
+            st = prefill_impl(ctx, cache, layer, seq, q_rows, out_rows, count, first_position + start, &local, false,
+                              attend_on, k_rows, v_rows, &ahead);
             if (st != HC_OK) return st;
-            const cudaError_t err = cudaEventRecord(cache->step_done[slot], s);
+            const cudaError_t err = cudaEventRecord(cache->step_done[slot], attend_on);
             if (err != cudaSuccess) return check_cuda(err, "prefill chunks: step event");
         } else {
+            if (other_used) {
+                // A chunk outside the pipeline (a last chunk of one token) follows everything before it.
+                const cudaError_t err = cudaStreamWaitEvent(s, cache->step_done[1], 0);
+                if (err != cudaSuccess) return check_cuda(err, "prefill chunks: join event");
+            }
             st = hc_layer_step(ctx, cache, layer, seq, q_rows, k_rows, v_rows, out_rows, count, first_position + start, &local, stream);
             if (st != HC_OK) return st;
         }
+    }
+    if (other_used) {
+        // The caller's stream ends behind the chunks that ran on the other one.
+        const cudaError_t err = cudaStreamWaitEvent(s, cache->step_done[1], 0);
+        if (err != cudaSuccess) return check_cuda(err, "prefill chunks: join event");
     }
     return HC_OK;
 }

@@ -104,6 +104,11 @@ struct Workspace {
     float* part_ml = nullptr;    // fp32 [rows][slots][2]
     size_t part_o_floats = 0;    // capacities
     size_t part_ml_floats = 0;
+    // What a prefill launch can need of the two (segment partials or second-fold state): the buffers
+    // hold it twice, so that two chunks' attention launches may be in flight at once, the second one
+    // working in the upper halves [prefill_o_floats, 2 prefill_o_floats) and likewise for part_ml.
+    size_t prefill_o_floats = 0;
+    size_t prefill_ml_floats = 0;
 };
 
 }  // namespace hc
