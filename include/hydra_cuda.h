@@ -425,8 +425,12 @@ HC_API hc_status hc_layer_step(hc_context* ctx, hc_kv_cache* cache, int layer, i
 
 /* hc_layer_step for a whole prompt: `tokens` tokens in chunks of `chunk` (the reference's
  * PrefillRunner loop, Sources/HydraMetal/PrefillRunner.swift:128-184, one call per prompt instead of
- * one per chunk).  Each chunk is one hc_layer_step, enqueued in order on `stream`; the results are
- * bit for bit those of the chunk-by-chunk calls. */
+ * one per chunk).  Each chunk is one hc_layer_step and the results are bit for bit those of the
+ * chunk-by-chunk calls.  The work starts behind whatever `stream` holds at the call and `stream` ends
+ * behind all of it, like any other call; in between, on layers with linear storage, the library
+ * runs a chunk's prologue one chunk ahead and alternate chunks' attention on two streams of its
+ * own (ordered by events), so that a chunk's kernels start while the previous chunk's are still
+ * finishing. */
 HC_API hc_status hc_prefill_chunks(hc_context* ctx, hc_kv_cache* cache, int layer, int seq,
                                    const void* q, const void* k, const void* v, void* out,
                                    int tokens, int first_position, int chunk,
