@@ -113,9 +113,9 @@ hc_status check_positions(const hc_kv_cache* cache, const hc_layer_store& L, int
         return fail(HC_KV_OVERFLOW, "position " + std::to_string(first + tokens - 1) + " beyond capacity " +
                                         std::to_string(cache->context_length));
     }
-    if (L.ring > 0 && tokens > L.ring - L.desc.window) {
+    if (L.ring > 0 && tokens > L.ring_margin) {
         return fail(HC_KV_OVERFLOW, "a chunk of " + std::to_string(tokens) + " tokens overruns the ring's margin of " +
-                                        std::to_string(L.ring - L.desc.window));
+                                        std::to_string(L.ring_margin));
     }
     if (p->rope && first + tokens > p->rope->positions) {
         return fail(HC_DIM_MISMATCH, "rope table is shorter than the positions asked for");
@@ -619,7 +619,14 @@ hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n
             ring = true;
         } else if (L.desc.storage != HC_STORAGE_LINEAR) { st = fail(HC_INVALID_ARGUMENT, "unknown storage"); break; }
         if (ring && sequence) { st = fail(HC_UNSUPPORTED, "ring storage cannot be sequence-sharded"); break; }
-        L.ring = ring ? round_up(L.desc.window + prefill_chunk, kTileKeys) : 0;
+        // The reference's ring holds window + prefill_chunk rows (KVCache.swift:160-167; here rounded up
+        // to whole tiles): that is what the margin, the reported ring size and the rewind floor
+        // follow.  The stored ring is one margin longer, so that the rows a chunk appends never
+        // overwrite keys the previous chunk still attends to and hc_prefill_chunks may run a chunk's
+        // prologue while the previous chunk's attention is finishing.
+        const int reference_ring = ring ? round_up(L.desc.window + prefill_chunk, kTileKeys) : 0;
+        L.ring_margin = ring ? reference_ring - L.desc.window : 0;
+        L.ring = ring ? round_up(reference_ring + L.ring_margin, kTileKeys) : 0;
         int tiles = (context_length + kTileKeys - 1) / kTileKeys;
         if (sequence) tiles = (tiles + sd.world - 1) / sd.world;
         L.capacity = ring ? L.ring : tiles * kTileKeys;
@@ -748,7 +755,7 @@ hc_status hc_kv_layer_info(const hc_kv_cache* cache, int layer, hc_layer_info* o
     const hc_layer_store& L = cache->layers[size_t(layer)];
     out->keys = L.k;
     out->values = L.v;
-    out->ring_size = L.ring;
+    out->ring_size = L.ring > 0 ? L.desc.window + L.ring_margin : 0;
     out->capacity = L.capacity;
     out->entry_bytes = L.keeps_history ? L.desc.kv_heads * L.desc.head_dim * 2 : 0;
     out->windowed = L.desc.window > 0 ? 1 : 0;
@@ -864,7 +871,7 @@ hc_status hc_kv_rewind_floor(const hc_kv_cache* cache, int seq, int* floor) {
     int margin = -1;
     for (const hc_layer_store& L : cache->layers) {
         if (L.keeps_history && L.ring > 0) {
-            const int m = L.ring - L.desc.window;
+            const int m = L.ring_margin;
             margin = margin < 0 ? m : std::min(margin, m);
         }
     }
@@ -1135,14 +1142,15 @@ hc_status hc_prefill_chunks(hc_context* ctx, hc_kv_cache* cache, int layer, int 
     if (tokens <= 0 || chunk <= 0) return fail(HC_INVALID_ARGUMENT, "tokens and chunk must be positive");
     const int d = params->head_dim;
     const int mult = params->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
-    // On a linear (non-ring) layer a chunk's prologue (K/V append, query norm and rotation) touches
-    // nothing the previous chunk's attention reads, apart from the prepared-query buffer, which has
-    // two slots: it runs on a stream of its own, one chunk ahead, in the SMs the attention kernel
-    // leaves idle while its last thread blocks finish.  (On a ring the appended rows overwrite keys
-    // the previous chunk still attends to.)
+    // A chunk's prologue (K/V append, query norm and rotation) touches nothing the previous chunk's
+    // attention reads, apart from the prepared-query buffer, which has two slots: it runs on a stream
+    // of its own, one chunk ahead, in the SMs the attention kernel leaves idle while its last thread
+    // blocks finish.  (A ring is stored one margin longer than the reference's, so the rows of chunk
+    // i + 1 land on positions older than any key chunk i attends to.)
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const hc_layer_store& L = cache->layers[size_t(layer)];
-    const bool ahead_ok = L.ring == 0 && chunk > 1 && chunk <= cache->ws.qprep_tokens && tokens > chunk && cache->copy_in != nullptr;
+    const bool ahead_ok = chunk > 1 && chunk <= cache->ws.qprep_tokens && tokens > chunk && cache->copy_in != nullptr &&
+                          (L.ring == 0 || L.ring >= L.desc.window + 2 * chunk);
     // Nor does a chunk's attention read anything the previous chunk's attention writes (the workspace
     // for segment partials and second-fold state exists twice): the chunks alternate between the
     // caller's stream and a second one, and a chunk's thread blocks take over the SMs as the previous

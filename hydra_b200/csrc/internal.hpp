@@ -134,7 +134,9 @@ struct hc_layer_store {
     hc_layer_desc desc{};
     uint16_t* k = nullptr;
     uint16_t* v = nullptr;
-    int ring = 0;
+    int ring = 0;                 // rows of the ring as stored (0: linear); positions map to pos % ring
+    int ring_margin = 0;          // the reference's ring is window + ring_margin rows: what a chunk may
+                                  // append at once and how far a rewind may reach
     int capacity = 0;
     int log_segment = 0;          // key tiles per segment, as a power of two (see common.cuh)
     bool keeps_history = false;

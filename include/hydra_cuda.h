@@ -208,8 +208,10 @@ HC_API hc_status hc_rms_norm(hc_context* ctx, const void* x, const void* scale_b
 /* Replaces KVCache.init(model:contextLength:device:) (Sources/HydraMetal/KVCache.swift:132-182).
  * Allocates, per layer, K and V as bf16 [max_seqs][kv_heads][capacity][head_dim] (head-major, so
  * one head's history is contiguous), zero-filled, plus the split-attention workspace.
- * `prefill_chunk` is KVCache.prefillChunk (512 in the reference): a ring holds
- * window + prefill_chunk rows, rounded up to a multiple of 128.  `shard` may be NULL.
+ * `prefill_chunk` is KVCache.prefillChunk (512 in the reference): a ring reports, and bounds chunks
+ * and rewinds by, window + prefill_chunk rows rounded up to a multiple of 128; it is stored one such
+ * margin longer (hc_layer_info.capacity), which lets hc_prefill_chunks overlap consecutive chunks.
+ * `shard` may be NULL.
  *
  * The call also fixes how each layer groups its 128-key tiles into segments (1024 or 4096 keys),
  * from the layer's head counts, prefill_chunk, max_seqs and the device's SM count: the attention

@@ -352,11 +352,11 @@ def test_kv_cache_bookkeeping_and_errors(hb, ctx):
               dict(q_heads=0, kv_heads=0, head_dim=0, window=0)]          # a recurrent layer
     cache = hb.KVCache(ctx, layers, 16384, prefill_chunk=512)
     sliding, full, recurrent = cache.layer(0), cache.layer(1), cache.layer(2)
-    assert sliding.ring_size == 640 and sliding.capacity == 640 and sliding.windowed == 1
+    assert sliding.ring_size == 640 and sliding.capacity == 1152 and sliding.windowed == 1   # stored one margin longer
     assert full.ring_size == 0 and full.capacity == 16384 and full.entry_bytes == 8 * 64 * 2
     assert recurrent.keeps_history == 0 and recurrent.entry_bytes == 0
     assert 2 * full.entry_bytes == 2048                                     # bytes per token per full layer
-    assert cache.byte_count == 2 * (640 + 16384) * 8 * 64 * 2
+    assert cache.byte_count == 2 * (1152 + 16384) * 8 * 64 * 2              # what is allocated: the ring as stored
     assert cache.visible_range(0, 5) == (0, 6)
     assert cache.visible_range(0, 1000) == (873, 128)
     assert cache.visible_range(1, 1000) == (0, 1001)
@@ -482,6 +482,42 @@ def test_whole_prompt_entry_points_equal_the_chunk_by_chunk_calls(hb, ctx, gated
     assert np.array_equal(outs["steps"], outs["host"])
     want = tl.oracle_path(q, k, v, np.arange(tokens), 0.125, 0, sinks=sinks, gate=gate, inv_freq=inv)
     assert tl.within_tolerance(outs["steps"], want)
+
+
+@pytest.mark.parametrize("d, qh, kvh", [(64, 16, 4), (256, 4, 2)])
+def test_prefill_chunks_on_a_ring_equals_the_chunk_by_chunk_calls(hb, ctx, d, qh, kvh):
+    """hc_prefill_chunks runs a chunk's prologue while the previous chunk's attention finishes and lets
+    consecutive chunks' attention launches overlap.  On a ring that is only right because the ring is
+    stored one margin longer than the window + chunk rows it reports; the prompt here wraps that ring
+    more than twice, and every chunk must equal its hc_layer_step and the oracle."""
+    rng = np.random.default_rng(907)
+    window, chunk, tokens = 256, 128, 2000
+    q = tl.normal_bf16(rng, (tokens, qh, d))
+    k = tl.normal_bf16(rng, (tokens, kvh, d))
+    v = tl.normal_bf16(rng, (tokens, kvh, d))
+    sinks = tl.normal_bf16(rng, (qh,))
+    outs = {}
+    for mode in ("steps", "chunks"):
+        layer = tl.Layer(hb, ctx, qh, kvh, d, 4096, window=window, sinks=sinks, prefill_chunk=chunk,
+                         storage=hb.capi.HC_STORAGE_RING)
+        assert layer.cache.layer(0).ring_size == window + chunk
+        dev = {name: tl.to_device(x) for name, x in (("q", q), ("k", k), ("v", v))}
+        out = tl.device_empty((tokens, qh, d))
+        if mode == "steps":
+            for start in range(0, tokens, chunk):
+                n = min(chunk, tokens - start)
+                layer.backend.layer_step(layer.cache, 0, dev["q"][start:], dev["k"][start:], dev["v"][start:],
+                                         out[start:], n, start, layer.params)
+        else:
+            for _ in range(2):          # twice: the second prompt starts over while the first one's tail may still run
+                layer.backend.prefill_chunks(layer.cache, 0, dev["q"], dev["k"], dev["v"], out, tokens, 0, chunk,
+                                             layer.params)
+        ctx.check()
+        outs[mode] = tl.to_host(out)
+        layer.close()
+    assert np.array_equal(outs["steps"], outs["chunks"])
+    want = tl.oracle_path(q, k, v, np.arange(tokens), 1 / np.sqrt(d), window, sinks=sinks)
+    assert tl.within_tolerance(outs["chunks"], want)
 
 
 @pytest.mark.parametrize("d,window", [(64, 0), (128, 96), (256, 0), (96, 0)])
