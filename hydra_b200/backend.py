@@ -209,9 +209,11 @@ class KVCache:
     linear_window_limit = 8192       # KVCache.linearWindowLimit
 
     def __init__(self, ctx: Context, layers: Sequence[dict], context_length: int,
-                 prefill_chunk: int = 512, max_seqs: int = 1, shard: Optional[tuple] = None):
+                 prefill_chunk: int = 512, max_seqs: int = 1, shard: Optional[tuple] = None,
+                 total_pages: int = 0):
         """`layers`: dicts with q_heads, kv_heads, head_dim, window (0 = full), storage (optional).
-        `shard`: (mode, rank, world) or None."""
+        `shard`: (mode, rank, world) or None.  `total_pages` > 0: the linear layers are pools of that
+        many 128-row pages shared by the sequences (hc_kv_cache_create_paged)."""
         self._lib = capi.load()
         self._ctx = ctx
         descs = (capi.LayerDesc * len(layers))()
@@ -220,15 +222,20 @@ class KVCache:
                                       layer.get("window", 0), layer.get("storage", capi.HC_STORAGE_AUTO))
         sd = capi.ShardDesc(*shard) if shard is not None else None
         handle = ctypes.c_void_p()
-        _check(self._lib.hc_kv_cache_create(ctx.handle, descs, len(layers), context_length,
-                                            prefill_chunk, max_seqs,
-                                            ctypes.byref(sd) if sd is not None else None,
-                                            ctypes.byref(handle)))
+        _check(self._lib.hc_kv_cache_create_paged(ctx.handle, descs, len(layers), context_length,
+                                                  prefill_chunk, max_seqs, total_pages,
+                                                  ctypes.byref(sd) if sd is not None else None,
+                                                  ctypes.byref(handle)))
         self.handle = handle
         self.layer_count = len(layers)
         self.context_length = context_length
         self.prefill_chunk = prefill_chunk
         self.max_seqs = max_seqs
+
+    @property
+    def free_pages(self) -> int:
+        """Free pages of a paged cache, -1 for a contiguous one."""
+        return int(self._lib.hc_kv_free_pages(self.handle))
 
     @property
     def byte_count(self) -> int:

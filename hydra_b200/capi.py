@@ -62,6 +62,9 @@ _PROTOTYPES = {
     "hc_inverse_frequencies": (c_int, [c_int, c_double, c_int, POINTER(c_double)]),
     "hc_kv_cache_create": (c_int, [_P, POINTER(LayerDesc), c_int, c_int, c_int, c_int,
                                    POINTER(ShardDesc), POINTER(_P)]),
+    "hc_kv_cache_create_paged": (c_int, [_P, POINTER(LayerDesc), c_int, c_int, c_int, c_int, c_int,
+                                         POINTER(ShardDesc), POINTER(_P)]),
+    "hc_kv_free_pages": (c_int, [_P]),
     "hc_kv_cache_destroy": (None, [_P]),
     "hc_kv_cache_bytes": (c_size_t, [_P]),
     "hc_kv_layer_info": (c_int, [_P, c_int, POINTER(LayerInfo)]),

@@ -72,6 +72,9 @@ CacheView view_of(const hc_kv_cache* cache, const hc_layer_store& L) {
     view.map.rank = sequence ? cache->shard.rank : 0;
     view.map.world = sequence ? cache->shard.world : 1;
     view.map.log_segment = L.log_segment;
+    const bool paged = cache->pages_dev != nullptr && L.ring == 0;
+    view.map.pages = paged ? cache->pages_dev : nullptr;
+    view.map.pages_per_seq = paged ? cache->pages_per_seq : 0;
     return view;
 }
 
@@ -187,6 +190,43 @@ bool use_tensor_path(const hc_attn_params* p, const AttnShape& shape, hc_status*
 // The body shared by hc_attention_prefill and hc_attention_prefill_partial.
 // With k_fused / v_fused set (hc_layer_step; one pass, tokens <= the prologue workspace) the K/V
 // append of the same tokens rides in the Q prologue's launch.
+// Paged storage: every 128-key tile of [first, first + tokens) of `seq` gets a page (all layers share
+// the table, so whichever layer appends a position first assigns it), and the new entries are copied
+// to the device table on `stream`, ahead of the kernel that writes the rows.
+hc_status ensure_pages(hc_kv_cache* cache, const hc_layer_store& L, int seq, int first, int tokens, cudaStream_t stream) {
+    if (!cache->pages_dev || L.ring != 0 || tokens <= 0) return HC_OK;
+    int* table = cache->pages_host + size_t(seq) * cache->pages_per_seq;
+    int lo = -1, hi = -1;
+    for (int tile = first / kTileKeys; tile <= (first + tokens - 1) / kTileKeys; ++tile) {
+        if (table[tile] >= 0) continue;
+        if (cache->free_pages.empty()) {
+            return fail(HC_KV_OVERFLOW, "the paged cache is out of pages (" + std::to_string(cache->total_pages) +
+                                            " of 128 rows): sequence " + std::to_string(seq) + " needs one for position " +
+                                            std::to_string(tile * kTileKeys));
+        }
+        table[tile] = cache->free_pages.back();
+        cache->free_pages.pop_back();
+        if (lo < 0) lo = tile;
+        hi = tile;
+    }
+    if (lo < 0) return HC_OK;
+    const size_t offset = size_t(seq) * cache->pages_per_seq + lo;
+    return check_cuda(cudaMemcpyAsync(cache->pages_dev + offset, cache->pages_host + offset, size_t(hi - lo + 1) * sizeof(int),
+                                      cudaMemcpyHostToDevice, stream), "page table update");
+}
+
+// Gives back the pages of `seq` from key tile `first_tile` on.
+void release_pages(hc_kv_cache* cache, int seq, int first_tile) {
+    if (!cache->pages_host) return;
+    int* table = cache->pages_host + size_t(seq) * cache->pages_per_seq;
+    for (int tile = std::max(first_tile, 0); tile < cache->pages_per_seq; ++tile) {
+        if (table[tile] >= 0) {
+            cache->free_pages.push_back(table[tile]);
+            table[tile] = -1;
+        }
+    }
+}
+
 // When `ahead` is given (hc_prefill_chunks), the prologue launch goes to ahead->stream into the
 // ahead->slot-th prepared-query buffer, and `stream` waits for ahead->done, recorded behind it: the
 // prologue of a chunk can then run while the previous chunk's attention is still finishing.
@@ -228,6 +268,10 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
             PrepArgs args{};
             fill_common(args, p);
             int jobs = 0;
+            if (k_fused) {
+                st = ensure_pages(cache, L, seq, first_position + start, count, ahead ? ahead->stream : stream);
+                if (st != HC_OK) return st;
+            }
             uint16_t* prepared = cache->ws.qprep + (ahead ? size_t(ahead->slot) * cache->ws.qprep_slot_elems : 0);
             if (prep) fill_q_job(args.job[jobs++], p, q_rows, prepared);
             if (k_fused) {
@@ -323,6 +367,10 @@ hc_status decode_impl(hc_context* ctx, hc_kv_cache* cache, int layer, const int*
             int jobs = 0;
             if (prep) fill_q_job(args.job[jobs++], p, q_rows, cache->ws.qprep);
             if (k_fused) {
+                for (int b = 0; b < count; ++b) {
+                    st = ensure_pages(cache, L, meta.seq[b], meta.pos[b], 1, stream);
+                    if (st != HC_OK) return st;
+                }
                 const size_t kv_row = size_t(p->kv_heads) * d;
                 fill_kv_jobs(args, jobs, p, offset_rows(k_fused, size_t(start), kv_row, p->io_dtype),
                              offset_rows(v_fused, size_t(start), kv_row, p->io_dtype));
@@ -565,7 +613,13 @@ hc_status hc_rope_table_pointers(const hc_rope_table* table, const float** cos_o
 
 hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n_layers, int context_length,
                              int prefill_chunk, int max_seqs, const hc_shard_desc* shard, hc_kv_cache** out) {
-    if (!ctx || !layers || !out || n_layers <= 0 || context_length <= 0 || prefill_chunk <= 0 || max_seqs <= 0) {
+    return hc_kv_cache_create_paged(ctx, layers, n_layers, context_length, prefill_chunk, max_seqs, 0, shard, out);
+}
+
+hc_status hc_kv_cache_create_paged(hc_context* ctx, const hc_layer_desc* layers, int n_layers, int context_length,
+                                   int prefill_chunk, int max_seqs, int total_pages, const hc_shard_desc* shard,
+                                   hc_kv_cache** out) {
+    if (!ctx || !layers || !out || n_layers <= 0 || context_length <= 0 || prefill_chunk <= 0 || max_seqs <= 0 || total_pages < 0) {
         return fail(HC_INVALID_ARGUMENT, "bad arguments to hc_kv_cache_create");
     }
     *out = nullptr;
@@ -578,6 +632,7 @@ hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n
         if (sd.world == 1) sd.mode = HC_SHARD_NONE;
     }
     const bool sequence = sd.mode == HC_SHARD_SEQUENCE;
+    if (sequence && total_pages > 0) return fail(HC_UNSUPPORTED, "a paged cache cannot be sequence-sharded");
     cudaError_t err = cudaSetDevice(ctx->device);
     if (err != cudaSuccess) return check_cuda(err, "cudaSetDevice");
 
@@ -593,6 +648,22 @@ hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n
 
     size_t max_q_elems = 0, max_kv_elems = 0, part_o_floats = 0, part_ml_floats = 0, prefill_o_floats = 0, prefill_ml_floats = 0;
     hc_status st = HC_OK;
+    if (total_pages > 0) {
+        cache->total_pages = total_pages;
+        cache->pages_per_seq = (context_length + kTileKeys - 1) / kTileKeys;
+        const size_t entries = size_t(max_seqs) * cache->pages_per_seq;
+        err = cudaMalloc(&cache->pages_dev, entries * sizeof(int));
+        if (err == cudaSuccess) err = cudaMemset(cache->pages_dev, 0, entries * sizeof(int));
+        if (err == cudaSuccess) err = cudaMallocHost(&cache->pages_host, entries * sizeof(int));
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            st = fail(HC_ALLOC_FAILED, std::string("page table: ") + cudaGetErrorString(err));
+        } else {
+            std::fill(cache->pages_host, cache->pages_host + entries, -1);
+            cache->free_pages.resize(size_t(total_pages));
+            for (int page = 0; page < total_pages; ++page) cache->free_pages[size_t(page)] = total_pages - 1 - page;
+        }
+    }
     for (int i = 0; i < n_layers && st == HC_OK; ++i) {
         hc_layer_store& L = cache->layers[size_t(i)];
         L.desc = layers[i];
@@ -629,8 +700,9 @@ hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n
         L.ring = ring ? round_up(reference_ring + L.ring_margin, kTileKeys) : 0;
         int tiles = (context_length + kTileKeys - 1) / kTileKeys;
         if (sequence) tiles = (tiles + sd.world - 1) / sd.world;
-        L.capacity = ring ? L.ring : tiles * kTileKeys;
-        const size_t bytes = size_t(max_seqs) * L.desc.kv_heads * L.capacity * d * 2;
+        const bool paged = total_pages > 0 && !ring;
+        L.capacity = ring ? L.ring : paged ? total_pages * kTileKeys : tiles * kTileKeys;
+        const size_t bytes = size_t(paged ? 1 : max_seqs) * L.desc.kv_heads * L.capacity * d * 2;
         err = cudaMalloc(&L.k, bytes);
         if (err == cudaSuccess) err = cudaMalloc(&L.v, bytes);
         if (err == cudaSuccess) err = cudaMemset(L.k, 0, bytes);
@@ -730,6 +802,8 @@ void hc_kv_cache_destroy(hc_kv_cache* cache) {
     if (cache->ws.part_o) cudaFree(cache->ws.part_o);
     if (cache->ws.part_ml) cudaFree(cache->ws.part_ml);
     if (cache->stage_dev) cudaFree(cache->stage_dev);
+    if (cache->pages_dev) cudaFree(cache->pages_dev);
+    if (cache->pages_host) cudaFreeHost(cache->pages_host);
     if (cache->copy_in) cudaStreamDestroy(cache->copy_in);
     if (cache->copy_out) cudaStreamDestroy(cache->copy_out);
     for (int i = 0; i < 2; ++i) {
@@ -745,9 +819,14 @@ size_t hc_kv_cache_bytes(const hc_kv_cache* cache) {
     if (!cache) return 0;
     size_t total = 0;
     for (const hc_layer_store& L : cache->layers) {
-        if (L.keeps_history) total += 2 * size_t(cache->max_seqs) * L.desc.kv_heads * L.capacity * L.desc.head_dim * 2;
+        const bool paged = cache->pages_dev != nullptr && L.ring == 0;      // one pool for all sequences
+        if (L.keeps_history) total += 2 * size_t(paged ? 1 : cache->max_seqs) * L.desc.kv_heads * L.capacity * L.desc.head_dim * 2;
     }
     return total;
+}
+
+int hc_kv_free_pages(const hc_kv_cache* cache) {
+    return cache && cache->pages_dev ? int(cache->free_pages.size()) : -1;
 }
 
 hc_status hc_kv_layer_info(const hc_kv_cache* cache, int layer, hc_layer_info* out) {
@@ -776,6 +855,27 @@ hc_status hc_kv_read(hc_context* ctx, const hc_kv_cache* cache, int layer, int s
     if (err != cudaSuccess) return check_cuda(err, "synchronise before reading the cache");
     const CacheView view = view_of(cache, L);
     const int d = L.desc.head_dim, heads = L.desc.kv_heads;
+    if (view.map.pages != nullptr) {
+        // Paged storage: row by row through the host's copy of the page table.
+        const int* table = cache->pages_host + size_t(seq) * cache->pages_per_seq;
+        for (int t = 0; t < tokens; ++t) {
+            const int pos = position + t;
+            const int page = table[pos / kTileKeys];
+            for (int h = 0; h < heads; ++h) {
+                const size_t dst = (size_t(t) * heads + h) * d;
+                if (page < 0) {
+                    if (keys_out) std::memset(keys_out + dst, 0, size_t(d) * 2);
+                    if (values_out) std::memset(values_out + dst, 0, size_t(d) * 2);
+                    continue;
+                }
+                const size_t src = (size_t(h) * L.capacity + size_t(page) * kTileKeys + pos % kTileKeys) * d;
+                if (keys_out) err = cudaMemcpy(keys_out + dst, L.k + src, size_t(d) * 2, cudaMemcpyDeviceToHost);
+                if (err == cudaSuccess && values_out) err = cudaMemcpy(values_out + dst, L.v + src, size_t(d) * 2, cudaMemcpyDeviceToHost);
+                if (err != cudaSuccess) return check_cuda(err, "reading the cache");
+            }
+        }
+        return HC_OK;
+    }
     if (L.ring == 0 && view.map.world <= 1 && tokens > 0) {
         // Linear storage: a head's rows are contiguous; one copy per head, then interleave on the host.
         std::vector<uint16_t> plane(size_t(tokens) * d);
@@ -817,7 +917,7 @@ int hc_shard_owner(int world, int position) {
 }
 
 int hc_shard_local_row(int world, int position) {
-    RowMap map{0, 0, world};
+    RowMap map{0, 0, world, 0, nullptr, 0};
     return row_of_position(map, position);
 }
 
@@ -862,6 +962,7 @@ hc_status hc_kv_advance(hc_kv_cache* cache, int seq, int tokens) {
 hc_status hc_kv_reset(hc_kv_cache* cache, int seq) {
     if (!seq_ok(cache, seq)) return fail(HC_INVALID_ARGUMENT, "bad arguments");
     cache->lengths[size_t(seq)] = 0;
+    release_pages(cache, seq, 0);
     return HC_OK;
 }
 
@@ -894,6 +995,7 @@ hc_status hc_kv_rewind(hc_kv_cache* cache, int seq, int tokens) {
                                        std::to_string(cache->lengths[size_t(seq)]) + ", floor " + std::to_string(floor) + ")");
     }
     cache->lengths[size_t(seq)] = tokens;
+    release_pages(cache, seq, (tokens + kTileKeys - 1) / kTileKeys);
     return HC_OK;
 }
 
@@ -907,6 +1009,8 @@ hc_status hc_kv_append(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
     if (!seq_ok(cache, seq)) return fail(HC_INVALID_ARGUMENT, "sequence index out of range");
     hc_layer_store& L = cache->layers[size_t(layer)];
     st = check_positions(cache, L, first_position, tokens, params);
+    if (st != HC_OK) return st;
+    st = ensure_pages(cache, L, seq, first_position, tokens, static_cast<cudaStream_t>(stream));
     if (st != HC_OK) return st;
     const size_t row = size_t(params->kv_heads) * params->head_dim;
     for (int start = 0; start < tokens; start += 32768) {
@@ -947,6 +1051,7 @@ hc_status hc_kv_append_batch(hc_context* ctx, hc_kv_cache* cache, int layer, con
         for (int b = 0; b < count; ++b) {
             if (!seq_ok(cache, seq_ids[start + b])) return fail(HC_INVALID_ARGUMENT, "sequence index out of range");
             st = check_positions(cache, L, positions[start + b], 1, params);
+            if (st == HC_OK) st = ensure_pages(cache, L, seq_ids[start + b], positions[start + b], 1, static_cast<cudaStream_t>(stream));
             if (st != HC_OK) return st;
             args.meta.seq[b] = seq_ids[start + b];
             args.meta.pos[b] = positions[start + b];

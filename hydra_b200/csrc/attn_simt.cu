@@ -232,7 +232,7 @@ __device__ inline void write_result(const EpilogueArgs& ep, size_t row, int q_he
 // ---- the first fold: one segment's tiles into a fold state ---------------------------------------
 // Runs tile_partial over the segment's tiles (ascending, `world` apart) and folds each into `st`,
 // which starts empty.  Queries of the G heads are in sm.q; [lo, hi] are the visible positions.
-__device__ void segment_partial(const SimtSmem& sm, const FoldState& st, const CacheView& cache, size_t head_rows,
+__device__ void segment_partial(const SimtSmem& sm, const FoldState& st, const CacheView& cache, int seq, size_t head_rows,
                                 const TileRange& tiles, int lo, int hi, int G, int d, float c) {
     for (int i = threadIdx.x; i < G * d; i += kThreads) st.A[i] = 0.0f;
     if (threadIdx.x < G) {
@@ -243,7 +243,7 @@ __device__ void segment_partial(const SimtSmem& sm, const FoldState& st, const C
     const int world = max(cache.map.world, 1);
     for (int j = 0; j < tiles.count; ++j) {
         const int tile = tiles.first + j * world;
-        const size_t row0 = head_rows + row_of_tile(cache.map, tile);
+        const size_t row0 = head_rows + cache_row(cache.map, seq, tile * kTileKeys);
         tile_partial(sm, cache.k + row0 * d, cache.v + row0 * d, tile * kTileKeys, lo, hi, G, d, c);
         for (int i = threadIdx.x; i < G * d; i += kThreads) {
             const int g = i / d;
@@ -283,7 +283,7 @@ decode_runs_kernel(const AttnShape shape, const CacheView cache, const BatchMeta
     FoldState st;
     SimtSmem sm = carve(raw, G, d, 1, &st);
     load_group_queries(sm, q + (size_t(b) * shape.q_heads + size_t(kv_head) * G) * d, G, d);
-    const size_t head_rows = (size_t(meta.seq[b]) * cache.kv_heads + kv_head) * cache.capacity;
+    const size_t head_rows = size_t(cache_plane(cache.map, meta.seq[b], cache.kv_heads, kv_head)) * cache.capacity;
     const size_t row0 = size_t(b) * shape.q_heads + size_t(kv_head) * G;
     if (tile_partials) {
         const int world = max(cache.map.world, 1);
@@ -291,7 +291,7 @@ decode_runs_kernel(const AttnShape shape, const CacheView cache, const BatchMeta
         __syncthreads();
         for (int j = 0; j < tiles.count; ++j) {
             const int tile = tiles.first + j * world;
-            const size_t krow = head_rows + row_of_tile(cache.map, tile);
+            const size_t krow = head_rows + cache_row(cache.map, meta.seq[b], tile * kTileKeys);
             tile_partial(sm, cache.k + krow * d, cache.v + krow * d, tile * kTileKeys, lo, position, G, d, shape.c);
             for (int i = threadIdx.x; i < G * d; i += kThreads) {
                 const int g = i / d;
@@ -305,7 +305,7 @@ decode_runs_kernel(const AttnShape shape, const CacheView cache, const BatchMeta
         }
         return;
     }
-    segment_partial(sm, st, cache, head_rows, tiles, lo, position, G, d, shape.c);
+    segment_partial(sm, st, cache, meta.seq[b], head_rows, tiles, lo, position, G, d, shape.c);
     const int slot = blockIdx.x;
     for (int i = threadIdx.x; i < G * d; i += kThreads) {
         const int g = i / d;
@@ -579,12 +579,12 @@ prefill_rows_kernel(const AttnShape shape, const CacheView cache, int seq,
     }
     __syncthreads();
 
-    const size_t head_rows = (size_t(seq) * cache.kv_heads + kv_head) * cache.capacity;
+    const size_t head_rows = size_t(cache_plane(cache.map, seq, cache.kv_heads, kv_head)) * cache.capacity;
     const int n_slots = visible_groups(position, position, shape.window, cache.map.log_segment);
     for (int slot = 0; slot < n_slots; ++slot) {
         const TileRange tiles = group_tiles(cache.map, position, position, shape.window, slot, cache.map.log_segment);
         if (tiles.count <= 0) continue;
-        segment_partial(sm, st[0], cache, head_rows, tiles, lo, position, G, d, shape.c);
+        segment_partial(sm, st[0], cache, seq, head_rows, tiles, lo, position, G, d, shape.c);
         for (int i = threadIdx.x; i < G * d; i += kThreads) {
             const int g = i / d;
             float Mn, a, b;

@@ -168,11 +168,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             bool ok = true;
             for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk)) {
                 const TcItem& w = walk.w;
-                const int plane = w.seq * args.kv_heads + w.kv_head;
+                const int plane = cache_plane(args.map, w.seq, args.kv_heads, w.kv_head);
                 for (int j = 0; j < w.n_tiles; ++j, ++t) {
                     const int slot = int(t % LT::kStages);
                     const uint32_t round = t / LT::kStages;
-                    const int row0 = row_of_tile(args.map, w.tile_first + j * world);
+                    const int row0 = cache_row(args.map, w.seq, (w.tile_first + j * world) * kTileKeys);
                     if (round > 0 && !mbar_wait(&bars->k_empty[slot], (round - 1) & 1, abort_flag, args.status, 1)) {
                         ok = false;
                         break;
@@ -223,8 +223,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                     break;
                 }
                 const TcItem& w = c.walk.w;
-                const int plane = w.seq * args.kv_heads + w.kv_head;
-                const int row0 = row_of_tile(args.map, w.tile_first + c.j * world);
+                const int plane = cache_plane(args.map, w.seq, args.kv_heads, w.kv_head);
+                const int row0 = cache_row(args.map, w.seq, (w.tile_first + c.j * world) * kTileKeys);
                 uint64_t* full = keys ? &bars->k_full[slot] : &bars->v_full[slot];
                 unsigned char* dst = (keys ? k_smem : v_smem) + slot * LT::kTileBytes;
                 mbar_expect_tx(full, LT::kTileBytes);
@@ -972,8 +972,9 @@ hc_status tc_make_tensor_maps(hc_kv_cache* cache, hc_layer_store& layer) {
     const int d = layer.desc.head_dim;
     for (int which = 0; which < 2; ++which) {
         CUtensorMap* map = new CUtensorMap;
+        const bool paged = cache->pages_dev != nullptr && layer.ring == 0;       // one plane per head, shared
         const cuuint64_t dims[3] = {cuuint64_t(d), cuuint64_t(layer.capacity),
-                                    cuuint64_t(cache->max_seqs) * layer.desc.kv_heads};
+                                    cuuint64_t(paged ? 1 : cache->max_seqs) * layer.desc.kv_heads};
         const cuuint64_t strides[2] = {cuuint64_t(d) * 2, cuuint64_t(layer.capacity) * d * 2};
         const cuuint32_t box[3] = {64, cuuint32_t(kTileKeys), 1};
         const cuuint32_t elem[3] = {1, 1, 1};

@@ -99,9 +99,9 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
             bool ok = true;
             for (TcItemIter walk = items_begin(args); ok && walk.item < args.n_items; items_next(args, walk)) {
                 const TcItem& w = walk.w;
-                const int plane = w.seq * args.kv_heads + w.kv_head;
+                const int plane = cache_plane(args.map, w.seq, args.kv_heads, w.kv_head);
                 for (int j = 0; j < w.n_tiles; ++j, ++t) {
-                    const int row0 = row_of_tile(args.map, w.tile_first + j * world);
+                    const int row0 = cache_row(args.map, w.seq, (w.tile_first + j * world) * kTileKeys);
                     if (t > 0 && !mbar_wait(&bars->k_empty, (t - 1) & 1, abort_flag, args.status, 1)) { ok = false; break; }
                     mbar_expect_tx(&bars->k_full, kTileBytes256);
                     for (int b = 0; b < kBlocks256; ++b) {

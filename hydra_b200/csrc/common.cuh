@@ -124,11 +124,15 @@ __device__ __forceinline__ void store_io(void* base, size_t index, int dtype, fl
 //                         tile j / world
 //   log_segment         : a segment is 2^log_segment consecutive tiles, absolute like the tiles
 //                         (3 or 5: 1024 or 4096 keys; fixed per layer when the cache is created)
+//   pages != null       : paged storage: the cache is a pool of 128-row pages shared by all sequences,
+//                         and key tile j of sequence s lives in page pages[s * pages_per_seq + j]
 struct RowMap {
     int ring;
     int rank;
     int world;
     int log_segment;
+    const int* pages;
+    int pages_per_seq;
 };
 constexpr int kLogSegmentSmall = 3;        // layers whose prefill launches need their rows' keys split
 constexpr int kLogSegmentLarge = 5;        // all others
@@ -184,6 +188,19 @@ __host__ __device__ __forceinline__ TileRange segment_run_tiles(const RowMap& ma
 // All the key tiles of this rank that rows at positions first_pos..last_pos see.
 __host__ __device__ __forceinline__ TileRange row_tiles(const RowMap& map, int first_pos, int last_pos, int window) {
     return owned_tiles(map, first_visible_tile(first_pos, window), last_pos / kTileKeys);
+}
+
+// Where sequence `seq`, kv head `kv_head` keeps position `pos`: the plane of the cache (rows of one
+// head) and the row inside it.  Contiguous storage gives every (sequence, head) a plane of its own;
+// paged storage one plane per head, shared by the sequences through the page table.
+__device__ __forceinline__ int cache_plane(const RowMap& map, int seq, int kv_heads, int kv_head) {
+    return map.pages != nullptr ? kv_head : seq * kv_heads + kv_head;
+}
+__device__ __forceinline__ int cache_row(const RowMap& map, int seq, int pos) {
+    if (map.pages != nullptr) {
+        return __ldg(map.pages + size_t(seq) * map.pages_per_seq + pos / kTileKeys) * kTileKeys + pos % kTileKeys;
+    }
+    return row_of_position(map, pos);
 }
 
 // First physical row of absolute tile j (callers only ask for tiles they own).

@@ -152,6 +152,14 @@ struct hc_kv_cache {
     int max_seqs = 0;
     hc_shard_desc shard{HC_SHARD_NONE, 0, 1};
     std::vector<int> lengths;
+    // Paged storage (hc_kv_cache_create_paged): the linear layers are pools of total_pages pages of 128
+    // rows shared by all sequences; one page table for all layers, [max_seqs][pages_per_seq], -1 =
+    // not assigned (the device copy holds 0 there: a valid page that no visible key maps to).
+    int total_pages = 0;
+    int pages_per_seq = 0;
+    int* pages_dev = nullptr;
+    int* pages_host = nullptr;    // pinned mirror, the source of the asynchronous updates
+    std::vector<int> free_pages;
     hc::Workspace ws;
     // hc_layer_step_host / hc_prefill_host: two device staging slots, a stream for the copies in and
     // one for the copies out, and the events that order them against the caller's stream.

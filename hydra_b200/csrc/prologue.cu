@@ -145,9 +145,9 @@ prepare_heads_vec_kernel(const PrepArgs args, int total_heads) {
             if (job.kind == 0) {
                 dst16 = reinterpret_cast<uint16_t*>(job.dst) + (size_t(token) * job.heads + head) * d;
             } else {
-                const int row = row_of_position(args.cache.map, position);
+                const int row = cache_row(args.cache.map, seq, position);
                 uint16_t* base = job.kind == 1 ? args.cache.k : args.cache.v;
-                dst16 = base + ((size_t(seq) * args.cache.kv_heads + head) * args.cache.capacity + row) * d;
+                dst16 = base + (size_t(cache_plane(args.cache.map, seq, args.cache.kv_heads, head)) * args.cache.capacity + row) * d;
             }
             *reinterpret_cast<uint2*>(dst16 + 4 * m) = pack_bf16x4(lo);
             *reinterpret_cast<uint2*>(dst16 + half + 4 * m) = pack_bf16x4(hi);
@@ -197,9 +197,9 @@ prepare_heads_kernel(const PrepArgs args) {
     if (job.kind == 0) {
         dst16 = reinterpret_cast<uint16_t*>(job.dst) + (size_t(token) * job.heads + head) * d;
     } else if (job.kind == 1 || job.kind == 2) {
-        const int row = row_of_position(args.cache.map, position);
+        const int row = cache_row(args.cache.map, seq, position);
         uint16_t* base = job.kind == 1 ? args.cache.k : args.cache.v;
-        dst16 = base + ((size_t(seq) * args.cache.kv_heads + head) * args.cache.capacity + row) * d;
+        dst16 = base + (size_t(cache_plane(args.cache.map, seq, args.cache.kv_heads, head)) * args.cache.capacity + row) * d;
     }
 
     // Stage the vector in shared memory.

@@ -222,6 +222,22 @@ HC_API hc_status hc_rms_norm(hc_context* ctx, const void* x, const void* scale_b
 HC_API hc_status hc_kv_cache_create(hc_context* ctx, const hc_layer_desc* layers, int n_layers,
                                     int context_length, int prefill_chunk, int max_seqs,
                                     const hc_shard_desc* shard, hc_kv_cache** out);
+/* The same cache with PAGED storage for its linear (full-attention) layers: instead of
+ * context_length rows per sequence, each such layer is one pool of `total_pages` pages of 128 rows
+ * (one key tile) shared by all max_seqs sequences, so a ragged batch costs the sum of its lengths
+ * rather than max_seqs times the longest.  A page is assigned when a position of its tile is first
+ * appended (by whichever layer gets there first: one page table serves all layers), and given back
+ * by hc_kv_reset and hc_kv_rewind; an append that finds no free page fails with HC_KV_OVERFLOW.
+ * Every other call is unchanged, and results are bit for bit those of the contiguous cache.  Ring
+ * layers keep their own rows per sequence.  The reference has no counterpart: its batches share one
+ * contiguous cache per slot (Sources/HydraMetal/KVCache.swift:132-182).  total_pages = 0 is
+ * hc_kv_cache_create.  Not for sequence-sharded caches. */
+HC_API hc_status hc_kv_cache_create_paged(hc_context* ctx, const hc_layer_desc* layers, int n_layers,
+                                          int context_length, int prefill_chunk, int max_seqs,
+                                          int total_pages, const hc_shard_desc* shard,
+                                          hc_kv_cache** out);
+/* Free pages of a paged cache, -1 for a contiguous one. */
+HC_API int hc_kv_free_pages(const hc_kv_cache* cache);
 HC_API void hc_kv_cache_destroy(hc_kv_cache* cache);
 
 /* Replaces KVCache.byteCount (KVCache.swift:184-187): bytes of K and V actually allocated. */
