@@ -478,6 +478,19 @@ class AttentionBackend:
                                    _ptr(residual) if residual is not None else None, _ptr(y), tokens, in_features,
                                    out_features, y_dtype, _stream(stream)))
 
+    def linear_group(self, x, weights, biases, ys, tokens: int, in_features: int, y_dtype: int = capi.HC_BF16,
+                     stream=None) -> None:
+        """Several projections of the same x in one launch (q_proj, k_proj, v_proj): lists of weights
+        [out_i][in_features], biases (entries may be None) and outputs [tokens][out_i]."""
+        n = len(weights)
+        arr = ctypes.c_void_p * n
+        w = arr(*[_ptr(t) for t in weights])
+        b = arr(*[(_ptr(t) if t is not None else None) for t in biases])
+        y = arr(*[_ptr(t) for t in ys])
+        outs = (ctypes.c_int * n)(*[int(t.shape[0]) for t in weights])
+        _check(self._lib.hc_linear_group(self.ctx.handle, _ptr(x), n, w, b, y, outs, tokens, in_features, y_dtype,
+                                         _stream(stream)))
+
     # rmsNorm (ForwardEncoder.swift:141): the layer's input norm over whole rows
     def rms_norm(self, x, scale, y, tokens: int, width: int, eps: float, x_dtype: int = capi.HC_F32,
                  y_dtype: int = capi.HC_BF16, stream=None) -> None:

@@ -1139,8 +1139,28 @@ hc_status hc_linear(hc_context* ctx, const void* x, const void* w, const void* b
     }
     if (residual && y_dtype != HC_F32) return fail(HC_INVALID_ARGUMENT, "hc_linear: a residual needs an fp32 y");
     if (tokens == 0) return HC_OK;
-    return linear_tc(ctx, x, w, bias, static_cast<const float*>(residual), y, tokens, in_features, out_features, y_dtype,
+    const float* res = static_cast<const float*>(residual);
+    return linear_tc(ctx, x, 1, &w, &bias, &res, &y, &out_features, tokens, in_features, y_dtype,
                      static_cast<cudaStream_t>(stream));
+}
+
+hc_status hc_linear_group(hc_context* ctx, const void* x, int n, const void* const* w, const void* const* bias,
+                          void* const* y, const int* out_features, int tokens, int in_features, int y_dtype, void* stream) {
+    if (!ctx || !x || !w || !y || !out_features) return fail(HC_INVALID_ARGUMENT, "null context or buffer");
+    if (n < 1 || n > 4) return fail(HC_INVALID_ARGUMENT, "hc_linear_group takes 1 to 4 projections");
+    if (tokens < 0 || in_features <= 0) return fail(HC_INVALID_ARGUMENT, "bad sizes");
+    if (y_dtype != HC_F32 && y_dtype != HC_BF16) return fail(HC_INVALID_ARGUMENT, "y_dtype must be HC_F32 or HC_BF16");
+    if (in_features % 64 != 0) {
+        return fail(HC_DIM_MISMATCH, "hc_linear_group: in_features " + std::to_string(in_features) + " must be a multiple of 64");
+    }
+    uintptr_t bits = reinterpret_cast<uintptr_t>(x);
+    for (int j = 0; j < n; ++j) {
+        if (!w[j] || !y[j] || out_features[j] <= 0) return fail(HC_INVALID_ARGUMENT, "hc_linear_group: null weight or output, or a bad width");
+        bits |= reinterpret_cast<uintptr_t>(w[j]) | reinterpret_cast<uintptr_t>(y[j]);
+    }
+    if (bits & 15) return fail(HC_INVALID_ARGUMENT, "hc_linear_group: x, w and y must be 16-byte aligned");
+    if (tokens == 0) return HC_OK;
+    return linear_tc(ctx, x, n, w, bias, nullptr, y, out_features, tokens, in_features, y_dtype, static_cast<cudaStream_t>(stream));
 }
 
 hc_status hc_rms_norm_heads(hc_context* ctx, void* vector, const void* weight_bf16, int tokens, int heads,

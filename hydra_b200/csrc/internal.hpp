@@ -236,8 +236,10 @@ hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_stor
                     const CacheView& cache, const BatchMeta& meta, int n_seq, const uint16_t* q,
                     const Workspace& ws, const EpilogueArgs& ep, cudaStream_t stream);
 // linear_tc.cu
-hc_status linear_tc(hc_context* ctx, const void* x, const void* w, const void* bias, const float* residual, void* y,
-                    int tokens, int in_features, int out_features, int y_dtype, cudaStream_t stream);
+// n_jobs (1 to 4) projections of the same x in one launch; bias / residual may be null, or hold nulls.
+hc_status linear_tc(hc_context* ctx, const void* x, int n_jobs, const void* const* w, const void* const* bias,
+                    const float* const* residual, void* const* y, const int* out_features, int tokens, int in_features,
+                    int y_dtype, cudaStream_t stream);
 // attn_tc256.cu (args_ptr: the TcArgs of tc_common.cuh)
 hc_status launch_tc256(hc_context* ctx, const void* tmap_k, const void* tmap_v, const void* args_ptr,
                        int n_items, cudaStream_t stream);

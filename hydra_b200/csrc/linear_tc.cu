@@ -13,6 +13,7 @@
 // One persistent CTA per SM walks the output tiles (all row tiles of one 256-wide column tile are
 // adjacent in the walk, so the CTAs running at one time share a weight tile in L2):
 //   warp 0      TMA producer: x tile (128 x 64) and w tile (256 x 64) per K step into a 4-stage ring
+//               (a launch may carry up to four projections of the same x: one list of tiles)
 //   warp 1      MMA issuer: four tcgen05.mma (M 128, N 256, K 16) per K step into one of two
 //               accumulators in tensor memory (2 x 256 columns)
 //   warps 4-7   epilogue: the finished accumulator from tensor memory, + bias (+ residual), to y (fp32 or bf16),
@@ -28,29 +29,67 @@ namespace hc {
 namespace {
 
 constexpr int kLinM = 128;
-constexpr int kLinN = 256;
 constexpr int kLinK = 64;                       // one 128-byte swizzled row of bf16
-constexpr int kLinStages = 4;
 constexpr int kLinABytes = kLinM * kLinK * 2;   // 16 KB
-constexpr int kLinBBytes = kLinN * kLinK * 2;   // 32 KB
 constexpr int kLinThreads = 256;
+constexpr int kLinMaxStages = 9;
+
+// Two shapes of the same kernel.  Wide: 128 x 256 output tiles, 4 stages: tensor-bound, for prompts.
+// Narrow: 128 x 32 tiles, 9 stages: when there are at most 128 tokens (decode) the work is reading
+// the weight once, and narrow column tiles spread its rows over all SMs with enough of them in
+// flight (9 x 4 KB per SM).  An output element is the same sum in the same order in both, so a token
+// projected alone and inside a prompt gets the same bits.
+template <int BN>
+struct LinShape {
+    static constexpr int kStages = BN == 256 ? 4 : kLinMaxStages;
+    static constexpr int kBBytes = BN * kLinK * 2;
+    static constexpr int kTmemCols = BN == 256 ? 512 : 64;      // two accumulators
+    static constexpr int kSmemBytes = 1024 + kStages * (kLinABytes + kBBytes);
+};
 
 struct LinBarriers {
-    uint64_t full[kLinStages], empty[kLinStages];
+    uint64_t full[kLinMaxStages], empty[kLinMaxStages];
     uint64_t acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
 
-struct LinArgs {
+constexpr int kLinJobs = 4;
+
+// One launch may carry several projections of the same x (q, k and v of a layer): their output tiles
+// form one list, job after job.
+struct LinJob {
     const uint16_t* bias;     // bf16 [out_features] or null
     const float* residual;    // fp32 [tokens][out_features] added to the result, or null (may be y itself)
     void* y;                  // [tokens][out_features]
+    int out_features;
+    int first_tile;           // of this job in the launch's list; its tiles: column tile major, row tiles adjacent
+};
+
+struct LinArgs {
+    LinJob job[kLinJobs];
+    int n_jobs;
     int y_dtype;              // HC_F32 or HC_BF16
-    int tokens, out_features;
-    int tiles_m, tiles_n, k_steps;
+    int tokens;
+    int tiles_m, n_tiles, k_steps;
     int* status;
 };
+
+struct LinTile {
+    int job, tn, tm;
+};
+__device__ __forceinline__ LinTile decode_tile(const LinArgs& args, int tile) {
+    LinTile t;
+    t.job = 0;
+    #pragma unroll
+    for (int j = 1; j < kLinJobs; ++j) {
+        if (j < args.n_jobs && tile >= args.job[j].first_tile) t.job = j;
+    }
+    const int local = tile - args.job[t.job].first_tile;
+    t.tn = local / args.tiles_m;
+    t.tm = local - t.tn * args.tiles_m;
+    return t;
+}
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
     asm volatile(
@@ -59,9 +98,15 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
         : "memory");
 }
 
+template <int BN>
 __global__ void __launch_bounds__(kLinThreads, 1)
-linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                 const LinArgs args) {
+linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w0,
+                 const __grid_constant__ CUtensorMap tmap_w1, const __grid_constant__ CUtensorMap tmap_w2,
+                 const __grid_constant__ CUtensorMap tmap_w3, const LinArgs args) {
+    using LS = LinShape<BN>;
+    constexpr int kLinN = BN;
+    constexpr int kLinStages = LS::kStages;
+    constexpr int kLinBBytes = LS::kBBytes;
     extern __shared__ unsigned char raw_smem[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
     unsigned char* a_smem = base;                                   // [stages][128 x 64]
@@ -84,10 +129,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         bars->abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == 1) tmem_alloc(&bars->tmem_base, 512);
+    if (warp == 1) tmem_alloc(&bars->tmem_base, LS::kTmemCols);
     if (warp == 0 && lane == 0) {
         prefetch_tensormap(&tmap_x);
-        prefetch_tensormap(&tmap_w);
+        prefetch_tensormap(&tmap_w0);
     }
     tc_fence_before();
     __syncthreads();
@@ -95,21 +140,23 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     const uint32_t tmem = bars->tmem_base;
     pdl_wait();
 
-    const int n_tiles = args.tiles_m * args.tiles_n;
+    const int n_tiles = args.n_tiles;
     if (warp == 0) {
         // ===== producer =====
         if (lane == 0) {
             uint32_t step = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
-                const int tn = tile / args.tiles_m, tm = tile - tn * args.tiles_m;
+                const LinTile where = decode_tile(args, tile);
+                const int tn = where.tn, tm = where.tm;
+                const CUtensorMap* tmap_w = where.job == 0 ? &tmap_w0 : where.job == 1 ? &tmap_w1 : where.job == 2 ? &tmap_w2 : &tmap_w3;
                 for (int k = 0; k < args.k_steps; ++k, ++step) {
                     const int slot = int(step % kLinStages);
                     const uint32_t round = step / kLinStages;
                     if (round > 0 && !mbar_wait(&bars->empty[slot], (round - 1) & 1, abort_flag, args.status, 21)) { ok = false; break; }
                     mbar_expect_tx(&bars->full[slot], kLinABytes + kLinBBytes);
                     tma_load_2d(a_smem + slot * kLinABytes, &tmap_x, &bars->full[slot], k * kLinK, tm * kLinM);
-                    tma_load_2d(b_smem + slot * kLinBBytes, &tmap_w, &bars->full[slot], k * kLinK, tn * kLinN);
+                    tma_load_2d(b_smem + slot * kLinBBytes, tmap_w, &bars->full[slot], k * kLinK, tn * kLinN);
                 }
             }
         }
@@ -150,7 +197,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const uint32_t lane_base = uint32_t(quad * 32) << 16;
         uint32_t count = 0;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++count) {
-            const int tn = tile / args.tiles_m, tm = tile - tn * args.tiles_m;
+            const LinTile where = decode_tile(args, tile);
+            const int tn = where.tn, tm = where.tm;
+            const LinJob& job = args.job[where.job];
             const int acc = int(count & 1);
             if (!mbar_wait(&bars->acc_full[acc], (count >> 1) & 1, abort_flag, args.status, 24)) break;
             tc_fence_after();
@@ -162,32 +211,32 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 HC_TMEM_LD32(tmem + lane_base + acc * kLinN + chunk * 32, v);
                 tc_wait_ld();
                 const int col0 = tn * kLinN + chunk * 32;
-                if (row_ok && col0 < args.out_features) {
+                if (row_ok && col0 < job.out_features) {
                 float r[32];
                 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int col = col0 + i;
-                    const float b = (args.bias != nullptr && col < args.out_features) ? bf16_bits_to_float(__ldg(args.bias + col)) : 0.0f;
+                    const float b = (job.bias != nullptr && col < job.out_features) ? bf16_bits_to_float(__ldg(job.bias + col)) : 0.0f;
                     r[i] = __fadd_rn(__uint_as_float(v[i]), b);
                 }
-                const size_t offset = size_t(row) * args.out_features + col0;
-                if (args.residual != nullptr) {
+                const size_t offset = size_t(row) * job.out_features + col0;
+                if (job.residual != nullptr) {
                     #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        if (col0 + i < args.out_features) r[i] = __fadd_rn(r[i], __ldg(args.residual + offset + i));
+                        if (col0 + i < job.out_features) r[i] = __fadd_rn(r[i], __ldg(job.residual + offset + i));
                     }
                 }
-                const bool whole = col0 + 32 <= args.out_features && (args.out_features & 7) == 0;
+                const bool whole = col0 + 32 <= job.out_features && (job.out_features & 7) == 0;
                 if (args.y_dtype == HC_F32) {
-                    float* dst = reinterpret_cast<float*>(args.y) + offset;
+                    float* dst = reinterpret_cast<float*>(job.y) + offset;
                     if (whole) {
                         #pragma unroll
                         for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(r[i], r[i + 1], r[i + 2], r[i + 3]);
                     } else {
-                        for (int i = 0; i < 32 && col0 + i < args.out_features; ++i) dst[i] = r[i];
+                        for (int i = 0; i < 32 && col0 + i < job.out_features; ++i) dst[i] = r[i];
                     }
                 } else {
-                    uint16_t* dst = reinterpret_cast<uint16_t*>(args.y) + offset;
+                    uint16_t* dst = reinterpret_cast<uint16_t*>(job.y) + offset;
                     if (whole) {
                         #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
@@ -199,7 +248,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                             *reinterpret_cast<uint4*>(dst + i) = packed;
                         }
                     } else {
-                        for (int i = 0; i < 32 && col0 + i < args.out_features; ++i) dst[i] = float_to_bf16_bits(r[i]);
+                        for (int i = 0; i < 32 && col0 + i < job.out_features; ++i) dst[i] = float_to_bf16_bits(r[i]);
                     }
                 }
                 }
@@ -217,40 +266,97 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, 512);
+    if (warp == 1) tmem_dealloc(tmem, LS::kTmemCols);
 }
 
 }  // namespace
 
-hc_status linear_tc(hc_context* ctx, const void* x, const void* w, const void* bias, const float* residual, void* y,
-                    int tokens, int in_features, int out_features, int y_dtype, cudaStream_t stream) {
-    CUtensorMap tmap_x, tmap_w;
-    hc_status st = tc_encode_2d(&tmap_x, x, uint64_t(tokens), uint64_t(in_features), kLinM);
-    if (st == HC_OK) st = tc_encode_2d(&tmap_w, w, uint64_t(out_features), uint64_t(in_features), kLinN);
+// Encoding a tensor map costs a few microseconds of host time, as much as a decode-sized call's
+// kernel; weights and activation buffers recur from call to call, so the last maps are kept, keyed
+// by what determines them.  One caller thread per context: the cache is per thread.
+static hc_status cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    struct Entry {
+        const void* base;
+        uint64_t rows, cols;
+        uint32_t box_rows;
+        CUtensorMap map;
+    };
+    constexpr int kEntries = 32;
+    static thread_local Entry entries[kEntries];
+    static thread_local int used = 0, next = 0;
+    for (int i = 0; i < used; ++i) {
+        const Entry& e = entries[i];
+        if (e.base == base && e.rows == rows && e.cols == cols && e.box_rows == box_rows) {
+            *out = e.map;
+            return HC_OK;
+        }
+    }
+    Entry& e = entries[next];
+    const hc_status st = tc_encode_2d(&e.map, base, rows, cols, box_rows);
+    if (st != HC_OK) {
+        e.base = nullptr;
+        return st;
+    }
+    e.base = base;
+    e.rows = rows;
+    e.cols = cols;
+    e.box_rows = box_rows;
+    *out = e.map;
+    next = (next + 1) % kEntries;
+    used = std::min(used + 1, kEntries);
+    return HC_OK;
+}
+
+template <int BN>
+static hc_status launch_linear(hc_context* ctx, const void* x, const void* const* w, LinArgs args, int in_features,
+                               cudaStream_t stream) {
+    using LS = LinShape<BN>;
+    CUtensorMap tmap_x, tmap_w[kLinJobs];
+    hc_status st = cached_map(&tmap_x, x, uint64_t(args.tokens), uint64_t(in_features), kLinM);
+    args.tiles_m = (args.tokens + kLinM - 1) / kLinM;
+    int tiles = 0;
+    for (int j = 0; j < kLinJobs && st == HC_OK; ++j) {
+        const int source = j < args.n_jobs ? j : 0;            // unused maps repeat the first
+        st = cached_map(&tmap_w[j], w[source], uint64_t(args.job[source].out_features), uint64_t(in_features), BN);
+        if (j < args.n_jobs) {
+            args.job[j].first_tile = tiles;
+            tiles += args.tiles_m * ((args.job[j].out_features + BN - 1) / BN);
+        }
+    }
     if (st != HC_OK) return st;
-    LinArgs args{};
-    args.bias = static_cast<const uint16_t*>(bias);
-    args.residual = residual;
-    args.y = y;
-    args.y_dtype = y_dtype;
-    args.tokens = tokens;
-    args.out_features = out_features;
-    args.tiles_m = (tokens + kLinM - 1) / kLinM;
-    args.tiles_n = (out_features + kLinN - 1) / kLinN;
-    args.k_steps = in_features / kLinK;
-    args.status = ctx->status_dev;
-    const int smem = 1024 + kLinStages * (kLinABytes + kLinBBytes) + int(sizeof(LinBarriers));
+    args.n_tiles = tiles;
+    const int smem = LS::kSmemBytes + int(sizeof(LinBarriers));
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
-        cudaError_t err = cudaFuncSetAttribute(linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t err = cudaFuncSetAttribute(linear_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (err != cudaSuccess) return check_cuda(err, "linear_tc_kernel shared memory");
         configured[ctx->device & 63] = true;
     }
-    const int grid = std::max(1, std::min(args.tiles_m * args.tiles_n, std::max(ctx->sm_count, 1)));
-    const cudaError_t launched = launch_pdl(linear_tc_kernel, grid, kLinThreads, size_t(smem), stream, tmap_x, tmap_w, args);
+    const int grid = std::max(1, std::min(tiles, std::max(ctx->sm_count, 1)));
+    const cudaError_t launched = launch_pdl(linear_tc_kernel<BN>, grid, kLinThreads, size_t(smem), stream, tmap_x, tmap_w[0],
+                                            tmap_w[1], tmap_w[2], tmap_w[3], args);
     ctx->launches += 1;
     if (launched != cudaSuccess) return check_cuda(launched, "linear_tc_kernel launch");
     return check_cuda(cudaGetLastError(), "linear_tc_kernel launch");
+}
+
+hc_status linear_tc(hc_context* ctx, const void* x, int n_jobs, const void* const* w, const void* const* bias,
+                    const float* const* residual, void* const* y, const int* out_features, int tokens, int in_features,
+                    int y_dtype, cudaStream_t stream) {
+    LinArgs args{};
+    args.n_jobs = n_jobs;
+    for (int j = 0; j < n_jobs; ++j) {
+        args.job[j].bias = bias ? static_cast<const uint16_t*>(bias[j]) : nullptr;
+        args.job[j].residual = residual ? residual[j] : nullptr;
+        args.job[j].y = y[j];
+        args.job[j].out_features = out_features[j];
+    }
+    args.y_dtype = y_dtype;
+    args.tokens = tokens;
+    args.k_steps = in_features / kLinK;
+    args.status = ctx->status_dev;
+    if (tokens <= kLinM) return launch_linear<32>(ctx, x, w, args, in_features, stream);
+    return launch_linear<256>(ctx, x, w, args, in_features, stream);
 }
 
 }  // namespace hc

@@ -7,7 +7,7 @@ returns HIDDEN STATES instead of tokens and logits and runs, per layer, the atte
 ReferenceLayer.decode (Sources/HydraReference/ReferenceLayer.swift:126-187):
 
     normed = rms_norm(hidden, input_norm)                      hc_rms_norm
-    q, k, v = normed W_q^T + b_q, ...                           hc_linear x 3
+    q, k, v = normed W_q^T + b_q, ...                           hc_linear_group (one launch)
     rotate q and k, append k and v, attend (sinks, window)      hc_layer_step
     hidden += attention W_o^T + b_o                             hc_linear with the residual
 
@@ -107,9 +107,8 @@ class AttentionStackRunner:
         attended = torch.empty((n, q_dim), device="cuda", dtype=bf)
         for layer, (w, params) in enumerate(zip(self.weights, self.params)):
             be.rms_norm(hidden, w["input_norm"], normed, n, self.hidden, self.eps)
-            be.linear(normed, w["wq"], w["bq"], q, n, self.hidden, q_dim, y_dtype=capi.HC_BF16)
-            be.linear(normed, w["wk"], w["bk"], k, n, self.hidden, kv_dim, y_dtype=capi.HC_BF16)
-            be.linear(normed, w["wv"], w["bv"], v, n, self.hidden, kv_dim, y_dtype=capi.HC_BF16)
+            be.linear_group(normed, [w["wq"], w["wk"], w["wv"]], [w["bq"], w["bk"], w["bv"]], [q, k, v], n, self.hidden,
+                            y_dtype=capi.HC_BF16)
             be.layer_step(self.kv_cache, layer, q, k, v, attended, n, first_position, params)
             be.linear(attended, w["wo"], w["bo"], hidden, n, q_dim, self.hidden, y_dtype=capi.HC_F32, residual=hidden)
         return hidden

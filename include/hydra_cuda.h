@@ -196,6 +196,14 @@ HC_API hc_status hc_linear(hc_context* ctx, const void* x, const void* w, const 
                            const void* residual, void* y, int tokens, int in_features,
                            int out_features, int y_dtype, void* stream);
 
+/* Up to four projections of the same x in ONE launch (a layer's q_proj, k_proj and v_proj): w, bias,
+ * y and out_features are arrays of n entries (bias may be NULL, or hold NULLs).  The results are bit
+ * for bit those of n hc_linear calls; what it saves is launches, which is most of a decode-sized
+ * call, and the idle SMs of the narrow k and v projections in a prompt-sized one. */
+HC_API hc_status hc_linear_group(hc_context* ctx, const void* x, int n, const void* const* w,
+                                 const void* const* bias, void* const* y, const int* out_features,
+                                 int tokens, int in_features, int y_dtype, void* stream);
+
 /* y = x * rsqrt(mean(x^2) + eps) * scale over whole rows: the layer's input norm.  Replaces
  * ForwardEncoder.rmsNorm (Sources/HydraMetal/ForwardEncoder.swift:141-157) and the batched kernel
  * (Sources/HydraMetal/Shaders/batch.metal:184-218).  x fp32 or bf16 [tokens][width], scale bf16

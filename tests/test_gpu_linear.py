@@ -45,6 +45,60 @@ def test_linear_matches_the_oracle(tokens, n_in, n_out, with_bias, out_bf16):
     ctx.close()
 
 
+def test_linear_rows_do_not_depend_on_the_batch():
+    """A token's projection is the same bits whether it is projected alone (the narrow, many-staged
+    shape of the kernel, for decode), in a chunk of 100, or inside a prompt of 700 (the wide shape): the
+    invariant the attention kernels keep between prefill and decode, kept by the projections too."""
+    import hydra_b200 as hb
+    ctx = hb.Context(0)
+    backend = hb.AttentionBackend(ctx)
+    rng = np.random.default_rng(3)
+    tokens, n_in, n_out = 700, 2880, 1536
+    x = tl.to_device(tl.normal_bf16(rng, (tokens, n_in)))
+    w = tl.to_device(ho.bf16_round(rng.normal(0.0, 0.02, (n_out, n_in))))
+    b = tl.to_device(ho.bf16_round(rng.normal(0.0, 0.5, (n_out,))))
+    whole = tl.device_empty((tokens, n_out), dtype="f32")
+    backend.linear(x, w, b, whole, tokens, n_in, n_out)
+    chunk = tl.device_empty((100, n_out), dtype="f32")
+    backend.linear(x[300:], w, b, chunk, 100, n_in, n_out)
+    one = tl.device_empty((1, n_out), dtype="f32")
+    backend.linear(x[333:], w, b, one, 1, n_in, n_out)
+    ctx.check()
+    whole, chunk, one = tl.to_host(whole), tl.to_host(chunk), tl.to_host(one)
+    assert np.array_equal(whole[300:400], chunk)
+    assert np.array_equal(whole[333], one[0])
+    ctx.close()
+
+
+@pytest.mark.parametrize("tokens", [1, 77, 700])
+def test_linear_group_equals_the_separate_calls(tokens):
+    """q_proj, k_proj and v_proj of the same x in one launch: the bits of three hc_linear calls, with
+    widths that are not whole tiles and one projection without a bias."""
+    import hydra_b200 as hb
+    ctx = hb.Context(0)
+    backend = hb.AttentionBackend(ctx)
+    rng = np.random.default_rng(5)
+    n_in, widths = 2880, (4096, 512, 520)
+    x = tl.to_device(tl.normal_bf16(rng, (tokens, n_in)))
+    weights = [tl.to_device(ho.bf16_round(rng.normal(0.0, 0.02, (n, n_in)))) for n in widths]
+    biases = [tl.to_device(ho.bf16_round(rng.normal(0.0, 0.5, (n,)))) for n in widths]
+    biases[1] = None
+    for dtype, code in (("bf16", hb.capi.HC_BF16), ("f32", hb.capi.HC_F32)):
+        separate = [tl.device_empty((tokens, n), dtype=dtype) for n in widths]
+        grouped = [tl.device_empty((tokens, n), dtype=dtype) for n in widths]
+        for w, b, y in zip(weights, biases, separate):
+            backend.linear(x, w, b, y, tokens, n_in, w.shape[0], y_dtype=code)
+        before = ctx.launch_count
+        backend.linear_group(x, weights, biases, grouped, tokens, n_in, y_dtype=code)
+        assert ctx.launch_count - before == 1
+        ctx.check()
+        for a, b in zip(separate, grouped):
+            assert np.array_equal(tl.to_host(a), tl.to_host(b))
+    with pytest.raises(hb.HydraCudaError):
+        backend.linear_group(x, weights * 2, biases * 2, grouped * 2, tokens, n_in)
+    ctx.close()
+
+
 def test_linear_refuses_what_it_cannot_tile():
     import hydra_b200 as hb
     ctx = hb.Context(0)
