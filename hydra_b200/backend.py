@@ -186,6 +186,7 @@ class AttnParams:
     gate_layout: int = capi.HC_GATE_NONE
     gate: object = None
     kernel_path: int = capi.HC_PATH_AUTO
+    block_ends: object = None       # int32 [tokens] device buffer (blockEnds of BatchEncoder.attention), or None
     _keep: list = field(default_factory=list, repr=False)
 
     def struct(self) -> capi.AttnParamsStruct:
@@ -199,6 +200,7 @@ class AttnParams:
         s.rope = self.rope.handle if self.rope is not None else None
         s.gate_layout, s.gate = int(self.gate_layout), _ptr(self.gate)
         s.kernel_path = int(self.kernel_path)
+        s.block_ends = _ptr(self.block_ends)
         return s
 
 

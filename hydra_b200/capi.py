@@ -38,6 +38,7 @@ class AttnParamsStruct(ctypes.Structure):
         ("norm_q", c_int), ("norm_k", c_int), ("norm_v", c_int),
         ("q_norm_weight", c_void_p), ("k_norm_weight", c_void_p), ("norm_eps", c_float),
         ("rope", c_void_p), ("gate_layout", c_int), ("gate", c_void_p), ("kernel_path", c_int),
+        ("block_ends", c_void_p),
     ]
 
 

@@ -253,12 +253,19 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
     if (st != HC_OK) return st;
     const AttnShape shape = shape_of(cache, p, partial_mode);
     const CacheView view = view_of(cache, L);
-    const bool tensor = use_tensor_path(p, shape, &st);
+    bool tensor = use_tensor_path(p, shape, &st);
     if (st != HC_OK) return st;
     const int d = p->head_dim;
     const int mult = p->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
     const bool prep = needs_q_prepare(p);
-    const int step = prep ? cache->ws.qprep_tokens : tokens;
+    int step = prep ? cache->ws.qprep_tokens : tokens;
+    // Bidirectional blocks: the general kernel, chunk by chunk (a block ends with its token's chunk).
+    const int* blocks = p->block_ends;
+    if (blocks) {
+        if (p->kernel_path == HC_PATH_TENSOR) return fail(HC_UNSUPPORTED, "block_ends run on the general kernels, not HC_PATH_TENSOR");
+        tensor = false;
+        step = std::min(step, cache->prefill_chunk);
+    }
 
     for (int start = 0; start < tokens; start += step) {
         const int count = std::min(step, tokens - start);
@@ -318,7 +325,8 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
             }
             st = tc_prefill(ctx, shape, L, view, seq, q_bf16, count, first_position + start, ws, ep, stream);
         } else {
-            st = simt_prefill(ctx, shape, view, seq, q_bf16, count, first_position + start, ep, stream);
+            st = simt_prefill(ctx, shape, view, seq, q_bf16, count, first_position + start, ep, stream,
+                              blocks ? blocks + start : nullptr);
         }
         if (st != HC_OK) return st;
     }
@@ -1292,6 +1300,7 @@ hc_status hc_prefill_chunks(hc_context* ctx, hc_kv_cache* cache, int layer, int 
     for (int start = 0; start < tokens; start += chunk, ++index) {
         const int count = std::min(chunk, tokens - start);
         hc_attn_params local = *params;
+        if (params->block_ends) local.block_ends = params->block_ends + start;
         if (params->gate_layout == HC_GATE_SEPARATE) {
             local.gate = offset_rows(params->gate, size_t(start), size_t(params->q_heads) * d, params->io_dtype);
         }
@@ -1378,6 +1387,7 @@ static hc_status host_chunks(hc_context* ctx, hc_kv_cache* cache, int layer, int
         if (err == cudaSuccess) err = cudaStreamWaitEvent(s, cache->in_done[slot], 0);
         if (err != cudaSuccess) return check_cuda(err, "host to device copy");
         hc_attn_params local = *params;
+        if (params->block_ends) local.block_ends = params->block_ends + start;    // device memory, like the sinks
         if (sep_gate) local.gate = base + off_g;
         const hc_status st = hc_layer_step(ctx, cache, layer, seq, base, base + off_k, base + off_v, base + off_o, count,
                                            first_position + start, &local, s);

@@ -7,7 +7,8 @@
 //                         then the epilogue (also finishes the decode rows of the tcgen05 kernels)
 //   merge_rows_kernel     a warp per (query token, head): the second fold over the segment partials
 //                         of a prefill chunk that the tcgen05 kernels split
-//   prefill_rows_kernel   one CTA per (kv head, token): both folds in place
+//   prefill_rows_kernel   one CTA per (kv head, token): both folds in place; the only kernel that
+//                         takes bidirectional blocks (image tokens)
 //
 // decode = split over key tiles + merge replaces attention_decode / attention_decode_split /
 // attention_decode_merge (Sources/HydraMetal/Shaders/attention.metal:132-242, 307-452).
@@ -554,13 +555,18 @@ merge_rows_kernel(const AttnShape shape, const RowMap map, const MergeRows rows,
 // ---- prefill: one (kv head, token) per CTA: the first fold per segment, the second in place -------
 __global__ void __launch_bounds__(kThreads)
 prefill_rows_kernel(const AttnShape shape, const CacheView cache, int seq,
-                    const uint16_t* __restrict__ q, int first_position, const EpilogueArgs ep) {
+                    const uint16_t* __restrict__ q, int first_position, const EpilogueArgs ep,
+                    const int* __restrict__ block_ends, int appended) {
     extern __shared__ __align__(16) unsigned char raw[];
     const int G = shape.group, d = shape.head_dim;
     const int kv_head = blockIdx.x;
     const int token = blockIdx.y;
     const int position = first_position + token;
     const int lo = shape.window > 0 ? max(0, position - shape.window + 1) : 0;
+    // A token of a bidirectional block sees on to the block's end (batch.metal:351-352), as far as
+    // keys have been appended.
+    int hi = position;
+    if (block_ends != nullptr) hi = max(position, min(__ldg(block_ends + token), appended) - 1);
 
     FoldState st[2];                              // st[0]: the current segment; st[1]: the row
     SimtSmem sm = carve(raw, G, d, 2, st);
@@ -580,11 +586,11 @@ prefill_rows_kernel(const AttnShape shape, const CacheView cache, int seq,
     __syncthreads();
 
     const size_t head_rows = size_t(cache_plane(cache.map, seq, cache.kv_heads, kv_head)) * cache.capacity;
-    const int n_slots = visible_groups(position, position, shape.window, cache.map.log_segment);
+    const int n_slots = visible_groups(position, hi, shape.window, cache.map.log_segment);
     for (int slot = 0; slot < n_slots; ++slot) {
-        const TileRange tiles = group_tiles(cache.map, position, position, shape.window, slot, cache.map.log_segment);
+        const TileRange tiles = group_tiles(cache.map, position, hi, shape.window, slot, cache.map.log_segment);
         if (tiles.count <= 0) continue;
-        segment_partial(sm, st[0], cache, seq, head_rows, tiles, lo, position, G, d, shape.c);
+        segment_partial(sm, st[0], cache, seq, head_rows, tiles, lo, hi, G, d, shape.c);
         for (int i = threadIdx.x; i < G * d; i += kThreads) {
             const int g = i / d;
             float Mn, a, b;
@@ -636,7 +642,7 @@ __global__ void combine_ranks_kernel(const float* __restrict__ gathered, int wor
 
 hc_status simt_prefill(hc_context* ctx, const AttnShape& shape, const CacheView& cache, int seq,
                        const uint16_t* q, int tokens, int first_position, const EpilogueArgs& ep,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const int* block_ends) {
     if (tokens <= 0) return HC_OK;
     const size_t smem = simt_smem_bytes(shape.group, shape.head_dim, 2);
     cudaError_t err = cudaFuncSetAttribute(prefill_rows_kernel,
@@ -660,7 +666,7 @@ hc_status simt_prefill(hc_context* ctx, const AttnShape& shape, const CacheView&
         dim3 grid(shape.kv_heads, count);
         prefill_rows_kernel<<<grid, kThreads, smem, stream>>>(
             shape, cache, seq, q + size_t(start) * shape.q_heads * shape.head_dim,
-            first_position + start, sub);
+            first_position + start, sub, block_ends ? block_ends + start : nullptr, first_position + tokens);
         ctx->launches += 1;
         err = cudaGetLastError();
         if (err != cudaSuccess) return check_cuda(err, "prefill_rows_kernel launch");

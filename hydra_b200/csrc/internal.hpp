@@ -191,7 +191,7 @@ hc_status launch_output_gate(hc_context* ctx, void* output, const void* gate, si
 // attn_simt.cu
 hc_status simt_prefill(hc_context* ctx, const AttnShape& shape, const CacheView& cache, int seq,
                        const uint16_t* q, int tokens, int first_position, const EpilogueArgs& ep,
-                       cudaStream_t stream);
+                       cudaStream_t stream, const int* block_ends = nullptr);
 hc_status simt_decode(hc_context* ctx, const AttnShape& shape, const CacheView& cache,
                       const BatchMeta& meta, int n_seq, const uint16_t* q, const Workspace& ws,
                       const EpilogueArgs& ep, cudaStream_t stream);

@@ -132,6 +132,19 @@ typedef struct hc_attn_params {
     int gate_layout;         /* hc_gate_layout                                                      */
     const void* gate;        /* device, io_dtype, for HC_GATE_SEPARATE                              */
     int kernel_path;         /* hc_kernel_path                                                      */
+    /* Bidirectional blocks (an image's tokens see each other), the `blocks` buffer of
+     * attention_prefill (Sources/HydraMetal/Shaders/batch.metal:322-324, 340-352; `blockEnds` of
+     * BatchEncoder.attention, Sources/HydraMetal/BatchEncoder.swift:210-217).  Device memory, one entry
+     * per token of the call: the position one past the end of the block the token belongs to, or 0
+     * for an ordinary token; NULL = none.  A token at position p then sees [start, max(p + 1,
+     * block end)) with `start` still bounded by the window.  Prefill calls only (decode ignores it).
+     * The call is worked in chunks of at most the cache's prefill_chunk tokens and a block reaches no
+     * further than the end of its token's chunk, the last key appended by then (the reference reads
+     * on, into rows not yet written, when a chunk boundary cuts an image).  A call with the buffer
+     * runs on the general kernels, not on the tensor cores: its rows outside the blocks are bit for
+     * bit those of an HC_PATH_SIMT call without the buffer, and agree with the tensor-core kernels'
+     * rows as closely as the two paths always do (both within the parity bound of the reference). */
+    const int* block_ends;
 } hc_attn_params;
 
 /* ---- context -------------------------------------------------------------------------------- */

@@ -305,10 +305,26 @@ void ho_apply_output_gate(const double* output, const double* gate, size_t n, do
 //   out       [n_rows][q_heads][d]   double
 //
 // Rows are independent and are spread over `threads` host threads.
+//
+// ho_attention_rows_blocks takes, besides, one entry per row: the position one past the end of the
+// bidirectional block the row's token belongs to, or 0.  The reference's double-precision layers
+// have no such mask; the rule is the Metal kernel's own loop bound, keyCount = max(blockEnd,
+// position + 1) - start (Sources/HydraMetal/Shaders/batch.metal:340-352).
+void ho_attention_rows_blocks(const float* q, const int64_t* positions, const int64_t* block_ends, int n_rows,
+                              const float* k, const float* v, int q_heads, int kv_heads, int d, double sm_scale,
+                              int window, const double* sinks, const float* gate, int threads, double* out);
+
 void ho_attention_rows(const float* q, const int64_t* positions, int n_rows, const float* k,
                        const float* v, int q_heads, int kv_heads, int d, double sm_scale,
                        int window, const double* sinks, const float* gate, int threads,
                        double* out) {
+    ho_attention_rows_blocks(q, positions, nullptr, n_rows, k, v, q_heads, kv_heads, d, sm_scale, window, sinks, gate,
+                             threads, out);
+}
+
+void ho_attention_rows_blocks(const float* q, const int64_t* positions, const int64_t* block_ends, int n_rows,
+                              const float* k, const float* v, int q_heads, int kv_heads, int d, double sm_scale,
+                              int window, const double* sinks, const float* gate, int threads, double* out) {
     const int group = q_heads / kv_heads;
     parallel_for(n_rows * q_heads, threads, [&](int item) {
         const int row = item / q_heads;
@@ -321,8 +337,10 @@ void ho_attention_rows(const float* q, const int64_t* positions, int n_rows, con
         const float* qrow = q + (size_t(row) * q_heads + head) * d;
         for (int i = 0; i < d; ++i) query[size_t(i)] = double(qrow[i]);
         double* dest = out + (size_t(row) * q_heads + head) * d;
+        int last = position;
+        if (block_ends != nullptr && int(block_ends[row]) > position + 1) last = int(block_ends[row]) - 1;
         attend_row(query.data(), k + size_t(kv_head) * d, v + size_t(kv_head) * d,
-                   ptrdiff_t(kv_heads) * d, first, position, d, sm_scale, sinks != nullptr,
+                   ptrdiff_t(kv_heads) * d, first, last, d, sm_scale, sinks != nullptr,
                    sinks ? sinks[head] : 0.0, dest, logits);
         if (gate) {
             const float* grow = gate + (size_t(row) * q_heads + head) * d;

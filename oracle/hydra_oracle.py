@@ -209,10 +209,14 @@ def apply_output_gate(output, gate) -> np.ndarray:
 
 
 def attention_rows(q, positions, k, v, sm_scale, window=0, sinks=None, gate=None,
-                   threads: Optional[int] = None) -> np.ndarray:
+                   threads: Optional[int] = None, block_ends=None) -> np.ndarray:
     """The attention part of the three reference layers for a batch of query tokens.
 
     q [n][q_heads][d], k/v [history][kv_heads][d] (float32 holding bf16 values), positions [n].
+    block_ends [n] or None: one past the end of each token's bidirectional block, 0 for none: the
+    token then sees up to max(position + 1, block end) keys from the window's start, the loop bound
+    of attention_prefill (Sources/HydraMetal/Shaders/batch.metal:340-352); the double-precision
+    reference layers themselves have no block mask.
     Returns float64 [n][q_heads][d].
     """
     q, k, v = _f32(q), _f32(k), _f32(v)
@@ -220,15 +224,19 @@ def attention_rows(q, positions, k, v, sm_scale, window=0, sinks=None, gate=None
     kv_heads = k.shape[1]
     pos = np.ascontiguousarray(positions, dtype=np.int64)
     assert pos.size == n and int(pos.max(initial=0)) < k.shape[0]
+    ends = None
+    if block_ends is not None:
+        ends = np.ascontiguousarray(block_ends, dtype=np.int64)
+        assert ends.size == n and int(ends.max(initial=0)) <= k.shape[0]
     s = _f64(sinks) if sinks is not None else None
     g = _f32(gate) if gate is not None else None
     out = np.empty((n, q_heads, d), dtype=np.float64)
     if threads is None:
         threads = hardware_threads()
-    lib().ho_attention_rows(_p(q, _F), _p(pos, ctypes.c_int64), ctypes.c_int(n), _p(k, _F),
-                            _p(v, _F), ctypes.c_int(q_heads), ctypes.c_int(kv_heads),
-                            ctypes.c_int(d), _D(sm_scale), ctypes.c_int(window), _p(s, _D),
-                            _p(g, _F), ctypes.c_int(threads), _p(out, _D))
+    lib().ho_attention_rows_blocks(_p(q, _F), _p(pos, ctypes.c_int64), _p(ends, ctypes.c_int64), ctypes.c_int(n),
+                                   _p(k, _F), _p(v, _F), ctypes.c_int(q_heads), ctypes.c_int(kv_heads),
+                                   ctypes.c_int(d), _D(sm_scale), ctypes.c_int(window), _p(s, _D),
+                                   _p(g, _F), ctypes.c_int(threads), _p(out, _D))
     return out
 
 

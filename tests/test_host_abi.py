@@ -33,8 +33,8 @@ def test_library_exports_every_declared_symbol(hb):
 
 
 def test_struct_layout_matches_header(hb):
-    # hc_attn_params: 4 ints, float, int, ptr, 3 ints, (pad), 2 ptrs, float, (pad), ptr, int, (pad), ptr, int
-    assert ctypes.sizeof(hb.capi.AttnParamsStruct) == 104
+    # hc_attn_params: 4 ints, float, int, ptr, 3 ints, (pad), 2 ptrs, float, (pad), ptr, int, (pad), ptr, int, (pad), ptr
+    assert ctypes.sizeof(hb.capi.AttnParamsStruct) == 112
     assert ctypes.sizeof(hb.capi.LayerDesc) == 20
     assert ctypes.sizeof(hb.capi.LayerInfo) == 40
 
