@@ -480,6 +480,15 @@ class AttentionBackend:
                                    _ptr(residual) if residual is not None else None, _ptr(y), tokens, in_features,
                                    out_features, y_dtype, _stream(stream)))
 
+    def linear_sharded(self, shard, x, weight, bias, y, tokens: int, in_features: int, out_features: int,
+                       residual=None, scatter: bool = False, stream=None) -> None:
+        """The row-parallel output projection of a head-sharded layer: this rank's GEMM, then NCCL's sum
+        over the ranks into y (fp32), all-reduce or reduce-scatter over token rows."""
+        _check(self._lib.hc_linear_sharded(self.ctx.handle, shard.handle, _ptr(x), _ptr(weight),
+                                           _ptr(bias) if bias is not None else None,
+                                           _ptr(residual) if residual is not None else None, _ptr(y), tokens,
+                                           in_features, out_features, 1 if scatter else 0, _stream(stream)))
+
     def linear_group(self, x, weights, biases, ys, tokens: int, in_features: int, y_dtype: int = capi.HC_BF16,
                      stream=None) -> None:
         """Several projections of the same x in one launch (q_proj, k_proj, v_proj): lists of weights

@@ -104,6 +104,7 @@ _PROTOTYPES = {
     "hc_attention_prefill_sharded": (c_int, [_P, _P, _P, c_int, c_int, _P, _P, c_int, c_int,
                                              POINTER(AttnParamsStruct), _P]),
     "hc_linear": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
+    "hc_linear_sharded": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P]),
     "hc_linear_group": (c_int, [_P, _P, c_int, POINTER(_P), POINTER(_P), POINTER(_P), POINTER(c_int), c_int, c_int, c_int, _P]),
     "hc_rms_norm": (c_int, [_P, _P, _P, _P, c_int, c_int, c_float, c_int, c_int, _P]),
     "hc_rms_norm_heads": (c_int, [_P, _P, _P, c_int, c_int, c_int, c_float, c_int, _P]),

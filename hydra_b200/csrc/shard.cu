@@ -8,6 +8,10 @@
 // memory.  The partials are small (head_dim + 2 floats per query row and head, 16.5 KB per rank for
 // a Qwen-shaped decode step), so the collective is latency-bound and one call per step is the
 // whole cost.
+//
+// hc_linear_sharded is the other exchange of a sharded layer: the row-parallel output projection,
+// a GEMM per rank and NCCL's sum of the partial results (ReferenceLayer.decode's `hidden +=
+// attention W_o^T + b_o`, Sources/HydraReference/ReferenceLayer.swift:186-187, over ranks).
 
 #include <new>
 
@@ -84,7 +88,7 @@ hc_status hc_shard_create(hc_context* ctx, void* nccl_comm, int mode, int rank, 
     const bool exchanges = mode == HC_SHARD_SEQUENCE && world > 1;
     if (exchanges && !nccl_comm) return fail(HC_COMM_ERROR, "a sequence shard over several ranks needs an NCCL communicator");
 #ifdef HC_HAVE_NCCL
-    if (exchanges) {
+    if (nccl_comm && world > 1) {          // a head shard may bring one too, for hc_linear_sharded
         int count = 0, user_rank = -1;
         hc_status st = check_nccl(ncclCommCount(static_cast<ncclComm_t>(nccl_comm), &count), "ncclCommCount");
         if (st == HC_OK) st = check_nccl(ncclCommUserRank(static_cast<ncclComm_t>(nccl_comm), &user_rank), "ncclCommUserRank");
@@ -155,6 +159,43 @@ hc_status hc_attention_prefill_sharded(hc_context* ctx, hc_shard* shard, hc_kv_c
     st = hc_attention_prefill_partial(ctx, cache, layer, seq, q, shard->mine, tokens, first_position, params, stream);
     if (st != HC_OK) return st;
     return gather_and_combine(ctx, shard, tokens, q, out, params, stream);
+}
+
+// The output projection of a head-sharded layer: every rank holds the attention output of its own
+// heads, [tokens][in_features] with in_features = its heads x head_dim, and the matching columns of
+// W_o as a matrix of its own, [out_features][in_features].  Each rank's GEMM gives a partial sum of
+// every output element; rank 0's carries the bias and the residual; NCCL adds the partials on the
+// caller's stream.
+hc_status hc_linear_sharded(hc_context* ctx, hc_shard* shard, const void* x, const void* w, const void* bias,
+                            const void* residual, void* y, int tokens, int in_features, int out_features, int scatter,
+                            void* stream) {
+    if (!shard) return fail(HC_INVALID_ARGUMENT, "null shard");
+    const int world = shard->desc.world;
+    if (world <= 1) return hc_linear(ctx, x, w, bias, residual, y, tokens, in_features, out_features, HC_F32, stream);
+    if (!shard->comm) return fail(HC_COMM_ERROR, "hc_linear_sharded: the shard was created without an NCCL communicator");
+    if (scatter && tokens % world != 0) {
+        return fail(HC_DIM_MISMATCH, "hc_linear_sharded: " + std::to_string(tokens) + " tokens do not divide over " +
+                                         std::to_string(world) + " ranks");
+    }
+    const bool first = shard->desc.rank == 0;
+    hc_status st = hc_linear(ctx, x, w, first ? bias : nullptr, first ? residual : nullptr, y, tokens, in_features,
+                             out_features, HC_F32, stream);
+    if (st != HC_OK || tokens == 0) return st;
+#ifdef HC_HAVE_NCCL
+    float* sums = static_cast<float*>(y);
+    const size_t count = size_t(tokens) * size_t(out_features);
+    if (scatter) {
+        const size_t mine = count / size_t(world);
+        return check_nccl(ncclReduceScatter(sums, sums + size_t(shard->desc.rank) * mine, mine, ncclFloat, ncclSum,
+                                            static_cast<ncclComm_t>(shard->comm), static_cast<cudaStream_t>(stream)),
+                          "ncclReduceScatter of the output projection");
+    }
+    return check_nccl(ncclAllReduce(sums, sums, count, ncclFloat, ncclSum, static_cast<ncclComm_t>(shard->comm),
+                                    static_cast<cudaStream_t>(stream)),
+                      "ncclAllReduce of the output projection");
+#else
+    return fail(HC_UNSUPPORTED, "this build of the library has no NCCL");
+#endif
 }
 
 }  // extern "C"

@@ -402,8 +402,9 @@ HC_API hc_status hc_attention_combine(hc_context* ctx, const void* gathered, int
 
 /* This rank's place among the GPUs that share a model (no counterpart in the reference).
  * `nccl_comm` is an ncclComm_t the caller initialised (ncclCommInitRank) and keeps alive; it is
- * needed only for HC_SHARD_SEQUENCE over more than one rank (head shards exchange nothing inside
- * attention) and its size and rank must agree with `world` and `rank`: a mismatch, like any
+ * needed for HC_SHARD_SEQUENCE over more than one rank and for hc_linear_sharded (head shards
+ * exchange nothing inside attention and may pass NULL if they do not call it), and its size and
+ * rank must agree with `world` and `rank`: a mismatch, like any
  * inconsistent (mode, rank, world), is HC_COMM_ERROR.  `max_partial_bytes` is the largest
  * hc_attention_partial_bytes(params, rows) a sharded call will need; the exchange buffers
  * ((world + 1) times that) are allocated here, not on the step path. */
@@ -427,6 +428,22 @@ HC_API hc_status hc_attention_prefill_sharded(hc_context* ctx, hc_shard* shard, 
                                               int layer, int seq, const void* q, void* out,
                                               int tokens, int first_position,
                                               const hc_attn_params* params, void* stream);
+
+/* The output projection of a head-sharded layer (row-parallel o_proj).  x is this rank's attention
+ * output, bf16 [tokens][in_features] with in_features = its own heads x head_dim; w the matching
+ * columns of W_o held as a matrix of its own, bf16 [out_features][in_features]; y fp32
+ * [tokens][out_features] on every rank.  Each rank's hc_linear gives its partial sums into y (rank
+ * 0's with the bias and the residual, which may be y itself), then NCCL adds them on `stream` through
+ * the communicator the shard was created with (any hc_shard_mode):
+ *   scatter = 0  ncclAllReduce in place: every rank ends with the whole y, the same bits on all;
+ *   scatter = 1  ncclReduceScatter in place: rank r ends with rows [r * tokens / world, (r + 1) *
+ *                tokens / world) of y summed (tokens must divide); its other rows hold partials.
+ * A world of one is hc_linear.  The collective is NCCL's own kernel after the GEMM, not fused with
+ * it.  No counterpart in the reference, which runs on one device. */
+HC_API hc_status hc_linear_sharded(hc_context* ctx, hc_shard* shard, const void* x, const void* w,
+                                   const void* bias, const void* residual, void* y, int tokens,
+                                   int in_features, int out_features, int scatter, void* stream);
+
 
 /* Stand-alone forms of the element-wise kernels, for runners that call them one by one as the
  * reference does.  In place on `vector` (io_dtype).
