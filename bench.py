@@ -592,12 +592,34 @@ def run_cuda(args):
         lambda i: backend.attention(cache, 0, q_sets[i % n_sets][pos:], o_sets[i % n_sets][pos:], [pos], params,
                                     seq_ids=[i % n_sets], stream=stream), 16, warm=4)
     dec_us = ranks.max(typical(dec_ms) * 1e3)
+    # What the same timer reads for a kernel that does next to nothing (the input norm of one row): after
+    # the flush, code, arguments and tables all come from DRAM, and that is most of a small step's time.
+    one_row = torch.zeros(1, 2880, device="cuda")
+    one_scale = torch.ones(2880, device="cuda", dtype=torch.bfloat16)
+    one_out = torch.empty(1, 2880, device="cuda", dtype=torch.bfloat16)
+    floor_us = ranks.max(typical(Timer(stream, 256 << 20).run(
+        lambda i: backend.rms_norm(one_row, one_scale, one_out, 1, 2880, 1e-5, stream=stream), 16, warm=4)) * 1e3)
+    # The same decode call 32 times in a row without the flush: the 8 MB of K/V then sit in L2, so this is
+    # the step's latency, not an HBM figure.
+    burst = 32
+    b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for timed in (False, True):
+        if timed:
+            b0.record(stream)
+        for _ in range(burst):
+            backend.attention(cache, 0, q_sets[0][pos:], o_sets[0][pos:], [pos], params, seq_ids=[0], stream=stream)
+    b1.record(stream)
+    torch.cuda.synchronize()
+    resident_us = ranks.max(b0.elapsed_time(b1) * 1e3 / burst)
     dec_bytes_rank = wl.decode_bytes(cfg, pos, cfg.layers[0])
     dec_gbs = dec_bytes_rank * world / (dec_us * 1e-6) / 1e9
     decode = {"context": pos + 1, "us_per_step": dec_us, "kv_bytes_per_step": dec_bytes_rank * world,
               "kv_gbs": dec_gbs, "frac_of_8tbs": dec_gbs / (NOMINAL_HBM_GBS * world),
               "frac_of_measured": dec_gbs / (peaks["hbm_gbs"] * world),
-              "note": "call = q prologue + split kernel + merge; L2 flushed before each timed call"}
+              "timer_floor_us": floor_us, "us_per_step_l2_resident": resident_us,
+              "note": "call = q prologue + split kernel + merge; L2 flushed before each timed call.  timer_floor_us: a "
+                      "one-row hc_rms_norm under the same timer and flush; us_per_step_l2_resident: 32 calls back to "
+                      "back without the flush (K/V in L2: latency, not an HBM figure)"}
 
     # End to end: the same prompt through hc_prefill_host with pinned host buffers.
     host = {name: dev[name].cpu().pin_memory() for name in ("q", "k", "v")}

@@ -124,3 +124,35 @@ def test_sequence_split_partials_combine_to_the_oracle():
 def test_head_split_outputs_concatenate():
     results = _run(_head_worker)
     assert all(r[1] for r in results)
+
+
+def _output_projection_worker(rank, world, port, queue):
+    """The algebra of hc_linear_sharded: each rank projects its own heads' columns of the attention
+    output through the matching columns of W_o (bias and residual on rank 0 only); the sum over ranks
+    (all-reduce) is the whole layer's `hidden += o_proj`."""
+    import torch
+    import torch.distributed as dist
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    rng = np.random.default_rng(13)
+    tokens, q_dim, hidden = 12, 64, 40
+    attention = ho.bf16_round(rng.standard_normal((tokens, q_dim)).astype(np.float32))
+    w_o = ho.bf16_round(rng.normal(0.0, 0.1, (hidden, q_dim)).astype(np.float32))
+    b_o = ho.bf16_round(rng.standard_normal(hidden).astype(np.float32))
+    residual = rng.standard_normal((tokens, hidden))
+    cols = slice(rank * q_dim // world, (rank + 1) * q_dim // world)
+    partial = ho.linear(np.ascontiguousarray(attention[:, cols]), np.ascontiguousarray(w_o[:, cols]),
+                        b_o if rank == 0 else None)
+    if rank == 0:
+        partial = partial + residual
+    summed = torch.from_numpy(np.ascontiguousarray(partial))
+    dist.all_reduce(summed)
+    whole = residual + ho.linear(attention, w_o, b_o)
+    queue.put((rank, float(np.max(np.abs(summed.numpy() - whole))), summed.numpy()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_row_parallel_output_projection_sums_to_the_oracle():
+    results = _run(_output_projection_worker)
+    assert results[0][1] < 1e-12 and results[1][1] < 1e-12
+    assert np.array_equal(results[0][2], results[1][2])            # the all-reduce leaves every rank the same sums
