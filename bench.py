@@ -696,7 +696,7 @@ def run_case(args):
     import torch
     import hydra_b200 as hb
     case = args.case
-    if case == "linear":
+    if case in ("linear", "linear1"):
         return run_linear_case(args)
     d = 256 if case.endswith("256") or case == "c4" else 64
     qh, kvh = (16, 2) if case == "c4" else ((16, 8) if d == 256 else (64, 8))
@@ -748,14 +748,15 @@ def run_case(args):
 
 
 def run_linear_case(args):
-    """hc_linear on C2's q_proj for the whole prompt: 4096 tokens x 2880 -> 4096 (48 output tiles of
-    128 x 256 per 128 tokens; 96.6 GFLOP)."""
+    """hc_linear on C2's q_proj: 2880 -> 4096 for the whole prompt (`linear`: 4096 tokens, 48 output
+    tiles of 128 x 256 per 128 tokens, 96.6 GFLOP) or for one decode token (`linear1`: the narrow
+    shape, 128 tiles of 32 weight rows; the work is reading the 23.6 MB weight once)."""
     import torch
     import hydra_b200 as hb
     ctx = hb.Context(0)
     backend = hb.AttentionBackend(ctx)
     gen = torch.Generator(device="cuda").manual_seed(0)
-    tokens, n_in, n_out = 4096, 2880, 4096
+    tokens, n_in, n_out = (1 if args.case == "linear1" else 4096), 2880, 4096
     x = torch.randn(tokens, n_in, device="cuda", generator=gen).to(torch.bfloat16)
     w = (torch.randn(n_out, n_in, device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
     b = torch.randn(n_out, device="cuda", generator=gen).to(torch.bfloat16)
@@ -766,7 +767,8 @@ def run_linear_case(args):
     ctx.check()
     best = min(times)
     work = 2.0 * tokens * n_in * n_out
-    print(f"linear {tokens} x {n_in} -> {n_out}: {best * 1e3:.1f} us per call, {work / (best * 1e-3) / 1e12:.1f} TFLOP/s "
+    print(f"linear {tokens} x {n_in} -> {n_out}: {best * 1e3:.1f} us per call, {work / (best * 1e-3) / 1e12:.1f} TFLOP/s, "
+          f"{2.0 * n_in * n_out / (best * 1e-3) / 1e9:.0f} GB/s of weight "
           f"(median {statistics.median(times) * 1e3:.1f} us over {len(times)} calls)")
     ctx.close()
     return 0
@@ -780,7 +782,7 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="only the headline configuration (C2)")
-    ap.add_argument("--case", default=None, choices=["prefill", "decode", "prefill256", "decode256", "c4", "linear"])
+    ap.add_argument("--case", default=None, choices=["prefill", "decode", "prefill256", "decode256", "c4", "linear", "linear1"])
     ap.add_argument("--repeat", type=int, default=3)
     args = ap.parse_args()
     if args.case:

@@ -68,3 +68,35 @@ def test_attention_block_matches_the_composed_oracle():
     tl.record_margin("GPT-OSS attention block, 256-token prompt + 3 decode steps", got, want)
     layer.close()
     ctx.close()
+
+
+@pytest.mark.parametrize("tokens, width", [(1, 2880), (37, 2880), (5, 4096), (3, 2816), (4, 4100), (6, 130), (2, 8192)])
+@pytest.mark.parametrize("x_f32, out_bf16, scaled", [(True, True, True), (True, False, False), (False, True, True)])
+def test_rms_norm_rows_match_the_oracle(tokens, width, x_f32, out_bf16, scaled):
+    """hc_rms_norm (the layer's input norm, ReferenceOps.rmsNorm): rows read four elements per load
+    (widths that are multiples of 4 up to 4096) and element by element (the others), fp32 and bf16
+    on either side, with and without the scale."""
+    import hydra_b200 as hb
+    ctx = hb.Context(0)
+    backend = hb.AttentionBackend(ctx)
+    rng = np.random.default_rng(width + tokens)
+    x = rng.standard_normal((tokens, width)).astype(np.float32) * 3.0
+    if not x_f32:
+        x = ho.bf16_round(x)
+    scale = ho.bf16_round(1.0 + 0.2 * rng.standard_normal(width).astype(np.float32)) if scaled else None
+    xd = tl.to_device(x, "f32" if x_f32 else "bf16")
+    sd = tl.to_device(scale) if scaled else None
+    out = tl.device_empty((tokens, width), "bf16" if out_bf16 else "f32")
+    backend.rms_norm(xd, sd, out, tokens, width, 1e-5, x_dtype=hb.capi.HC_F32 if x_f32 else hb.capi.HC_BF16,
+                     y_dtype=hb.capi.HC_BF16 if out_bf16 else hb.capi.HC_F32)
+    ctx.check()
+    want = np.stack([ho.rms_norm(row, scale, 1e-5, use_sqrt=True) for row in x])
+    have = tl.to_host(out)
+    assert tl.within_tolerance(have, want, 1e-4, bf16_output=out_bf16)
+    # a row's result does not depend on the rows beside it
+    one = tl.device_empty((1, width), "bf16" if out_bf16 else "f32")
+    backend.rms_norm(xd[tokens - 1:], sd, one, 1, width, 1e-5, x_dtype=hb.capi.HC_F32 if x_f32 else hb.capi.HC_BF16,
+                     y_dtype=hb.capi.HC_BF16 if out_bf16 else hb.capi.HC_F32)
+    ctx.check()
+    assert np.array_equal(tl.to_host(one)[0], have[tokens - 1])
+    ctx.close()
