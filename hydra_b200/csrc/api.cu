@@ -253,19 +253,15 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
     if (st != HC_OK) return st;
     const AttnShape shape = shape_of(cache, p, partial_mode);
     const CacheView view = view_of(cache, L);
-    bool tensor = use_tensor_path(p, shape, &st);
+    const bool tensor = use_tensor_path(p, shape, &st);
     if (st != HC_OK) return st;
     const int d = p->head_dim;
     const int mult = p->gate_layout == HC_GATE_INTERLEAVED ? 2 : 1;
     const bool prep = needs_q_prepare(p);
     int step = prep ? cache->ws.qprep_tokens : tokens;
-    // Bidirectional blocks: the general kernel, chunk by chunk (a block ends with its token's chunk).
+    // Bidirectional blocks: chunk by chunk (a block ends with its token's chunk).
     const int* blocks = p->block_ends;
-    if (blocks) {
-        if (p->kernel_path == HC_PATH_TENSOR) return fail(HC_UNSUPPORTED, "block_ends run on the general kernels, not HC_PATH_TENSOR");
-        tensor = false;
-        step = std::min(step, cache->prefill_chunk);
-    }
+    if (blocks) step = std::min(step, cache->prefill_chunk);
 
     for (int start = 0; start < tokens; start += step) {
         const int count = std::min(step, tokens - start);
@@ -323,7 +319,8 @@ hc_status prefill_impl(hc_context* ctx, hc_kv_cache* cache, int layer, int seq, 
                 ws.part_o_floats = ws.prefill_o_floats;
                 ws.part_ml_floats = ws.prefill_ml_floats;
             }
-            st = tc_prefill(ctx, shape, L, view, seq, q_bf16, count, first_position + start, ws, ep, stream);
+            st = tc_prefill(ctx, shape, L, view, seq, q_bf16, count, first_position + start, ws, ep, stream,
+                            blocks ? blocks + start : nullptr);
         } else {
             st = simt_prefill(ctx, shape, view, seq, q_bf16, count, first_position + start, ep, stream,
                               blocks ? blocks + start : nullptr);

@@ -7,8 +7,8 @@
 //                         then the epilogue (also finishes the decode rows of the tcgen05 kernels)
 //   merge_rows_kernel     a warp per (query token, head): the second fold over the segment partials
 //                         of a prefill chunk that the tcgen05 kernels split
-//   prefill_rows_kernel   one CTA per (kv head, token): both folds in place; the only kernel that
-//                         takes bidirectional blocks (image tokens)
+//   prefill_rows_kernel   one CTA per (kv head, token): both folds in place (with bidirectional
+//                         blocks too, like the tcgen05 kernels)
 //
 // decode = split over key tiles + merge replaces attention_decode / attention_decode_split /
 // attention_decode_merge (Sources/HydraMetal/Shaders/attention.metal:132-242, 307-452).

@@ -370,8 +370,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const TcItem& w = walk.w;
             const bool valid = t_local < w.valid_tokens;
             const bool warp_has_rows = quad * 32 < (w.valid_tokens << args.log_group);   // warp-uniform
-            const int pos = valid ? w.first_pos + t_local : -1;
+            int pos = valid ? w.first_pos + t_local : -1;
             const int lo = args.window > 0 ? max(0, pos - args.window + 1) : 0;
+            // From here on `pos` is the last key the row sees: its own, or the end of its bidirectional
+            // block (Sources/HydraMetal/Shaders/batch.metal:351-352) as far as keys have been appended.
+            if (!args.decode && args.block_ends != nullptr && valid) {
+                pos = max(pos, min(__ldg(args.block_ends + (w.first_pos - args.first_position) + t_local), args.appended) - 1);
+            }
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
                 if (int(t & 1) != parity) continue;
                 const int sb = int(t % LT::kSBufs);
@@ -1058,7 +1063,7 @@ static hc_status launch_any(hc_context* ctx, const AttnShape& shape, const TcArg
 
 hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer, const CacheView& cache,
                      int seq, const uint16_t* q, int tokens, int first_position, const Workspace& ws,
-                     const EpilogueArgs& ep, cudaStream_t stream) {
+                     const EpilogueArgs& ep, cudaStream_t stream, const int* block_ends) {
     if (!layer.tmap_k || !layer.tmap_v) return fail(HC_UNSUPPORTED, "this layer has no tensor maps");
     if (tokens <= 0) return HC_OK;
     TcArgs args{};
@@ -1073,7 +1078,7 @@ hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_sto
     int slots = 1, most_tiles = 1;
     for (int mtile = 0; mtile < args.mtiles; ++mtile) {
         const int first = first_position + mtile * tokens_per_tile;
-        const int last = first_position + std::min((mtile + 1) * tokens_per_tile, tokens) - 1;
+        const int last = first_position + (block_ends ? tokens : std::min((mtile + 1) * tokens_per_tile, tokens)) - 1;
         slots = std::max(slots, visible_groups(first, last, shape.window, cache.map.log_segment));
         most_tiles = std::max(most_tiles, row_tiles(cache.map, first, last, shape.window).count);
     }
@@ -1091,7 +1096,12 @@ hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_sto
     const int item_cost = shape.head_dim == 256 ? 8 : 4;
     const int whole_time = ((whole_items + sms - 1) / sms) * (most_tiles + item_cost);
     const int split_time = ((whole_items * slots + sms - 1) / sms) * (std::min(most_tiles, 1 << cache.map.log_segment) + item_cost) + 10;
-    const bool whole = !can_split || (can_finish && whole_time <= split_time);
+    // With bidirectional blocks a row's last key is known on the device only: whole rows per item, no
+    // merge over per-row segment lists (or the general kernel, if the row state does not fit).
+    if (block_ends && !can_finish) return simt_prefill(ctx, shape, cache, seq, q, tokens, first_position, ep, stream, block_ends);
+    args.block_ends = block_ends;
+    args.appended = first_position + tokens;
+    const bool whole = block_ends != nullptr || !can_split || (can_finish && whole_time <= split_time);
     if (whole && !can_finish) {
         return fail(HC_KV_OVERFLOW, "prefill: the attention workspace is too small for this chunk (" + std::to_string(tokens) +
                                         " tokens over " + std::to_string(slots) + " segments)");

@@ -190,8 +190,12 @@ attention_tc256_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
             const TcItem& w = walk.w;
             const bool valid = t_local < w.valid_tokens;
             const bool warp_has_rows = quad * 32 < (w.valid_tokens << args.log_group);
-            const int pos = valid ? w.first_pos + t_local : -1;
+            int pos = valid ? w.first_pos + t_local : -1;
             const int lo = args.window > 0 ? max(0, pos - args.window + 1) : 0;
+            // From here on the last key the row sees: its own, or the end of its bidirectional block.
+            if (!args.decode && args.block_ends != nullptr && valid) {
+                pos = max(pos, min(__ldg(args.block_ends + (w.first_pos - args.first_position) + t_local), args.appended) - 1);
+            }
             for (int j = 0; j < w.n_tiles; ++j, ++t) {
                 const int sb = int(t & 1);
                 if (!mbar_wait(&bars->s_full[sb], (t >> 1) & 1, abort_flag, args.status, 8)) { ok = false; break; }

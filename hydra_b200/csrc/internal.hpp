@@ -231,7 +231,7 @@ hc_status tc_encode_2d(void* map, const void* base, uint64_t rows, uint64_t cols
 bool tc_supported(const AttnShape& shape);
 hc_status tc_prefill(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer,
                      const CacheView& cache, int seq, const uint16_t* q, int tokens,
-                     int first_position, const Workspace& ws, const EpilogueArgs& ep, cudaStream_t stream);
+                     int first_position, const Workspace& ws, const EpilogueArgs& ep, cudaStream_t stream, const int* block_ends = nullptr);
 hc_status tc_decode(hc_context* ctx, const AttnShape& shape, const hc_layer_store& layer,
                     const CacheView& cache, const BatchMeta& meta, int n_seq, const uint16_t* q,
                     const Workspace& ws, const EpilogueArgs& ep, cudaStream_t stream);

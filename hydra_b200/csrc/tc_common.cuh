@@ -52,6 +52,11 @@ struct TcArgs {
     unsigned short seq_run[kMaxBatch];   // segments per run of sequence b (decode, segment partials)
     uint32_t seq_magic[kMaxBatch];       // division by seq_slots[b]
     BatchMeta meta;
+    // Prefill with bidirectional blocks: per token of the call, one past the end of its block (0 =
+    // none), and the position one past the last key appended.  Every item then reaches to the last
+    // appended key's tile; rows that see nothing of a tile fold its empty partial, a no-op.
+    const int* block_ends;
+    int appended;
 };
 
 // n / d for the small operands of the item list: with magic = ceil(2^32 / d) the high word of
@@ -109,7 +114,7 @@ __device__ __forceinline__ TcItem decode_item(const TcArgs& args, int index) {
         w.first_pos = args.first_position + w.row0;
         w.seq = args.seq;
     }
-    const int last_pos = w.first_pos + w.valid_tokens - 1;
+    const int last_pos = (!args.decode && args.block_ends != nullptr) ? args.appended - 1 : w.first_pos + w.valid_tokens - 1;
     TileRange tiles;
     if (args.finish) {
         tiles = row_tiles(args.map, w.first_pos, last_pos, args.window);

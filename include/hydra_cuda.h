@@ -140,10 +140,10 @@ typedef struct hc_attn_params {
      * block end)) with `start` still bounded by the window.  Prefill calls only (decode ignores it).
      * The call is worked in chunks of at most the cache's prefill_chunk tokens and a block reaches no
      * further than the end of its token's chunk, the last key appended by then (the reference reads
-     * on, into rows not yet written, when a chunk boundary cuts an image).  A call with the buffer
-     * runs on the general kernels, not on the tensor cores: its rows outside the blocks are bit for
-     * bit those of an HC_PATH_SIMT call without the buffer, and agree with the tensor-core kernels'
-     * rows as closely as the two paths always do (both within the parity bound of the reference). */
+     * on, into rows not yet written, when a chunk boundary cuts an image).  The tensor-core kernels
+     * take the buffer (head_dim 64, 128, 256: whole rows per item, every item reaching to the chunk's
+     * last key tile), the general kernel the rest.  Rows outside the blocks keep, bit for bit, the
+     * results of the call without the buffer, and so still equal their decode steps. */
     const int* block_ends;
 } hc_attn_params;
 

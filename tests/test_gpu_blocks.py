@@ -2,7 +2,8 @@
 (Sources/HydraMetal/BatchEncoder.swift:210-217), the `blocks` buffer of attention_prefill
 (Sources/HydraMetal/Shaders/batch.metal:322-324, 340-352).  A token inside a block (an image's
 tokens) sees the whole block, forward as well as back; the window still bounds where its range
-starts.  The oracle applies the shader's loop bound to the reference's double-precision attention.
+starts.  The tensor-core kernels take the buffer for head_dim 64, 128 and 256, the general kernel for
+the rest.  The oracle applies the shader's loop bound to the reference's double-precision attention.
 """
 import dataclasses
 
@@ -71,19 +72,24 @@ def test_blocks_match_the_oracle(q_heads, kv_heads, d, window, prefix):
     # The mask did something: a block's first token differs from its causal self.
     causal = ho.attention_rows(q[prefix:], positions, k, v, layer.params.sm_scale, window)
     assert tl.max_abs(want[10], causal[10]) > 1e-3
-    # Tokens outside the blocks are untouched by it: bit for bit the general kernel's rows without
-    # the buffer, and the tensor-core kernels' rows within the tolerance the two paths agree to.
+    # Tokens outside the blocks are untouched by it: bit for bit the rows of the call without the
+    # buffer, on the tensor-core kernels (head_dim 64, 128, 256) and on the general ones (512, or forced).
     outside = ends == 0
-    general = prefill_with(layer, dataclasses.replace(layer.params, kernel_path=hb.capi.HC_PATH_SIMT), q[prefix:], prefix)
-    assert np.array_equal(have[outside], general[outside])
     plain = layer.prefill(q[prefix:], prefix)
-    assert tl.max_abs(have[outside], plain[outside]) < 2e-2
+    assert np.array_equal(have[outside], plain[outside])
+    simt = dataclasses.replace(layer.params, kernel_path=hb.capi.HC_PATH_SIMT)
+    general = prefill_with(layer, dataclasses.replace(simt, block_ends=params.block_ends), q[prefix:], prefix)
+    assert tl.within_tolerance(general, want, TOL)
+    assert np.array_equal(general[outside], prefill_with(layer, simt, q[prefix:], prefix)[outside])
+    assert tl.max_abs(have, general) < 2e-2             # the two paths agree as closely as they always do
     layer.close()
     ctx.close()
 
 
 def test_no_blocks_is_the_call_without_the_buffer():
-    """All entries 0: the rows of the general kernel without the buffer, bit for bit."""
+    """All entries 0: the rows of the call without the buffer, bit for bit, on either path (with the
+    buffer every item reaches to the chunk's last key tile and the rows fold the empty partials of the
+    tiles they do not see: a no-op)."""
     import hydra_b200 as hb
     ctx = hb.Context(0)
     rng = np.random.default_rng(8)
@@ -93,14 +99,17 @@ def test_no_blocks_is_the_call_without_the_buffer():
     k = tl.normal_bf16(rng, (tokens, kv_heads, d))
     v = tl.normal_bf16(rng, (tokens, kv_heads, d))
     layer.append(k, v, 0)
-    general = prefill_with(layer, dataclasses.replace(layer.params, kernel_path=hb.capi.HC_PATH_SIMT), q, 0)
-    params = dataclasses.replace(layer.params, block_ends=device_ints(np.zeros(tokens)))
-    assert np.array_equal(prefill_with(layer, params, q, 0), general)
-    assert tl.max_abs(general, layer.prefill(q, 0)) < 2e-2
-    out = tl.device_empty((tokens, q_heads, d))
-    with pytest.raises(hb.UnsupportedPattern):
-        forced = dataclasses.replace(params, kernel_path=hb.capi.HC_PATH_TENSOR)
-        layer.backend.attention_prefill(layer.cache, 0, tl.to_device(q), out, tokens, 0, forced)
+    zeros = device_ints(np.zeros(tokens))
+    for path in (hb.capi.HC_PATH_TENSOR, hb.capi.HC_PATH_SIMT):
+        params = dataclasses.replace(layer.params, kernel_path=path)
+        assert np.array_equal(prefill_with(layer, dataclasses.replace(params, block_ends=zeros), q, 0),
+                              prefill_with(layer, params, q, 0)), path
+    # and the decode step of a token outside any block still equals its prefill row
+    plain = layer.prefill(q, 0)
+    blocked = prefill_with(layer, dataclasses.replace(layer.params, block_ends=device_ints(block_map(0, tokens, [(40, 100)]))), q, 0)
+    for t in (10, 200, tokens - 1):
+        assert np.array_equal(layer.decode(q[t:t + 1], [t])[0], blocked[t]), t
+    assert np.array_equal(blocked[200], plain[200]) and not np.array_equal(blocked[40], plain[40])
     layer.close()
     ctx.close()
 
