@@ -97,3 +97,15 @@ def test_shard_description_is_checked_before_any_device_is_touched(hb):
     with pytest.raises(hb.HydraCudaError) as info:
         hb.Shard(None, hb.capi.HC_SHARD_SEQUENCE, 1, 2)
     assert info.value.status == hb.capi.HC_INVALID_ARGUMENT
+
+
+def test_projection_entry_points_check_their_arguments_on_the_host(hb):
+    """hc_linear, hc_linear_group, hc_linear_sharded and hc_rms_norm decide a null context, shard or
+    buffer before anything reaches a device: a status, never a crash."""
+    lib = hb.capi.load()
+    invalid = hb.capi.HC_INVALID_ARGUMENT
+    assert lib.hc_linear(None, None, None, None, None, None, 4, 64, 64, hb.capi.HC_F32, None) == invalid
+    assert lib.hc_linear_group(None, None, 3, None, None, None, None, 4, 64, hb.capi.HC_BF16, None) == invalid
+    assert lib.hc_linear_sharded(None, None, None, None, None, None, None, 4, 64, 64, 0, None) == invalid
+    assert lib.hc_rms_norm(None, None, None, None, 4, 64, 1e-5, hb.capi.HC_F32, hb.capi.HC_BF16, None) == invalid
+    assert b"null" in lib.hc_last_error_string()
